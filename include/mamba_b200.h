@@ -1,0 +1,178 @@
+/* C ABI of libmamba_b200.so: the selective-scan path of mamba.py as sm_100a CUDA kernels.
+ *
+ * The reference project is pure Python; its "interface" for this path is a handful of
+ * Python callables.  Each entry point below names the reference callable it replaces
+ * (path inside the reference project : lines).  The Python host layer of this repository
+ * binds these symbols with ctypes and mirrors the reference's call signatures on top.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer on the current CUDA device unless said otherwise.
+ *   - The caller owns every buffer (inputs, outputs, workspaces); nothing here allocates
+ *     or frees device memory, and nothing synchronises the device.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *   - Strides are in ELEMENTS.  The innermost dimension is always unit-stride.
+ *   - dtype codes: MB200_F32 = 0, MB200_BF16 = 1 for the activation tensors; the scan
+ *     state, A, D and all carries are always float32.
+ *   - Return value: 0 on success, a negative MB200_E* code otherwise (mb200_strerror()).
+ *     Nothing traps or aborts the device.
+ */
+#ifndef MAMBA_B200_H
+#define MAMBA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { MB200_F32 = 0, MB200_BF16 = 1 };
+
+enum {
+  MB200_OK = 0,
+  MB200_EINVAL = -1,      /* bad shape / null pointer / negative size            */
+  MB200_EDTYPE = -2,      /* unknown dtype code                                   */
+  MB200_ENSTATE = -3,     /* d_state N not one of the compiled sizes (4,8,16,32,64) */
+  MB200_EALIGN = -4,      /* a float32 state/carry pointer is not 16-byte aligned */
+  MB200_ELAUNCH = -5,     /* the CUDA runtime refused the launch                  */
+  MB200_ETOOBIG = -6,     /* size beyond a documented limit of the entry point    */
+  MB200_ESETUP = -7       /* per-device set-up of the library failed              */
+};
+
+/* Flags of mb200_sscan_fwd / mb200_sscan_bwd. */
+enum {
+  MB200_DELTA_SOFTPLUS = 1  /* delta = softplus(delta_raw + delta_bias[e]) is applied inside;
+                               without it `delta` is taken as already discretised           */
+};
+
+const char* mb200_strerror(int code);
+int mb200_version(void);
+
+/* Number of timesteps between two saved scan states ("chunk carries").  The carries
+ * tensor of the fused scan has shape (B, ceil(L / chunk), ED, N), float32. */
+int mb200_sscan_chunk(void);
+
+/* Number of L-segments the PScan kernels should be launched with for this problem size
+ * (1 = single pass).  With nseg > 1 the caller passes a float32 workspace `ws` of
+ * 2 * B * nseg * D*N elements to mb200_pscan_fwd / mb200_pscan_bwd. */
+int mb200_pscan_segments(int64_t B, int64_t L, int64_t DN);
+
+/* ---- PScan.apply forward: H[t] = A[t]*H[t-1] + X[t], H[-1] = 0, along L.
+ * Replaces mambapy/pscan.py:151-186 (PScan.forward) without padding L to a power of two
+ * and without touching the inputs.
+ * A, X, H: (B, L, D, N) with the (D, N) block dense; strides (sb, sl) per tensor.
+ * h0 (optional, may be NULL): (B, D*N) float32 incoming state; hT (optional): outgoing state. */
+int mb200_pscan_fwd(const void* A, const void* X, void* H,
+                    int64_t B, int64_t L, int64_t DN,
+                    int64_t a_sb, int64_t a_sl, int64_t x_sb, int64_t x_sl,
+                    int64_t h_sb, int64_t h_sl,
+                    const float* h0, float* hT, float* ws, int nseg, int dtype, void* stream);
+
+/* ---- PScan.apply backward.  Replaces mambapy/pscan.py:188-224 (PScan.backward):
+ * gradX[t] = gradH[t] + A[t+1]*gradX[t+1];  gradA[t] = H[t-1]*gradX[t], gradA[0] = 0
+ * (or h0*gradX[0] when an incoming state h0 is given).
+ * A, H, gradH in; gradA, gradX out; all (B, L, D, N) with dense (D, N) blocks. */
+int mb200_pscan_bwd(const void* A, const void* H, const void* gradH,
+                    void* gradA, void* gradX,
+                    int64_t B, int64_t L, int64_t DN,
+                    int64_t a_sb, int64_t a_sl, int64_t h_sb, int64_t h_sl,
+                    int64_t g_sb, int64_t g_sl, int64_t ga_sb, int64_t ga_sl,
+                    int64_t gx_sb, int64_t gx_sl,
+                    const float* h0, float* ws, int nseg, int dtype, void* stream);
+
+/* ---- Fused selective scan, forward.
+ * Replaces mambapy/mamba.py:274-295 (MambaBlock.selective_scan), :297-327
+ * (selective_scan_seq) and, when z != NULL, the gate of MambaBlock.forward (:229-231);
+ * with MB200_DELTA_SOFTPLUS also the softplus(delta + dt_bias) of MambaBlock.ssm (:264-265).
+ *   y[b,t,e] = ( sum_n C[b,t,n]*h[b,t,e,n] + D[e]*x[b,t,e] ) * silu(z[b,t,e])
+ *   h[b,t,e,n] = exp(delta[b,t,e]*A[e,n]) * h[b,t-1,e,n] + delta[b,t,e]*Bm[b,t,n]*x[b,t,e]
+ * x, delta, z, y: (B, L, ED) activations, strides (sb, sl) each.  Bm, Cm: (B, L, N).
+ * A: (ED, N) float32 dense.  D: (ED) float32 or NULL (treated as 0).
+ * h0 / hT: optional (B, ED, N) float32 incoming / outgoing state.
+ * carries: optional (B, ceil(L/chunk), ED, N) float32; entry c receives the state that
+ *          enters timestep c*chunk.  Needed by mb200_sscan_bwd. */
+int mb200_sscan_fwd(const void* x, const void* delta, const void* z,
+                    const float* A, const void* Bm, const void* Cm, const float* D,
+                    const float* delta_bias, const float* h0,
+                    void* y, float* hT, float* carries,
+                    int64_t B, int64_t L, int64_t ED, int N,
+                    int64_t x_sb, int64_t x_sl, int64_t d_sb, int64_t d_sl,
+                    int64_t z_sb, int64_t z_sl, int64_t b_sb, int64_t b_sl,
+                    int64_t c_sb, int64_t c_sl, int64_t y_sb, int64_t y_sl,
+                    int dtype, int flags, void* stream);
+
+/* ---- Fused selective scan, backward (the autograd the reference gets from PyTorch for
+ * mambapy/mamba.py:274-295 + :229-231 together with mambapy/pscan.py:188-224).
+ * Recomputes h chunk by chunk from `carries`, runs the reverse scan, and writes
+ *   dx, ddelta, dz : (B, L, ED) in the activation dtype (dz only when z != NULL)
+ *   dB, dC         : (B, L, N)  float32, ACCUMULATED into (caller zero-fills)
+ *   dA (ED, N), dD (ED), ddelta_bias (ED): float32, ACCUMULATED into (caller zero-fills)
+ * g_in (optional): (B, ED, N) float32, a[t_L]*g[t_L] arriving from the sequence that follows
+ *                  (sequence-sharded use); g_out (optional): the same quantity leaving t = 0.
+ * dh0 is g_out; dy is the gradient w.r.t. y. */
+int mb200_sscan_bwd(const void* x, const void* delta, const void* z,
+                    const float* A, const void* Bm, const void* Cm, const float* D,
+                    const float* delta_bias, const void* dy, const float* carries,
+                    const float* g_in,
+                    void* dx, void* ddelta, void* dz,
+                    float* dB, float* dC, float* dA, float* dD, float* ddelta_bias,
+                    float* g_out,
+                    int64_t B, int64_t L, int64_t ED, int N,
+                    int64_t x_sb, int64_t x_sl, int64_t d_sb, int64_t d_sl,
+                    int64_t z_sb, int64_t z_sl, int64_t b_sb, int64_t b_sl,
+                    int64_t c_sb, int64_t c_sl, int64_t dy_sb, int64_t dy_sl,
+                    int64_t dx_sb, int64_t dx_sl, int64_t dd_sb, int64_t dd_sl,
+                    int64_t dz_sb, int64_t dz_sl,
+                    int dtype, int flags, void* stream);
+
+/* ---- Fused decode step.  Replaces the arithmetic of mambapy/mamba.py:384-414
+ * (MambaBlock.ssm_step after the projections) and, with conv_w != NULL, also the
+ * conv-window part of MambaBlock.step (:366-369, :379) and its gate (:373-375).
+ *   xin   : (B, ED) activations.  With conv_w == NULL it is the post-conv, post-SiLU x.
+ *           With conv_w != NULL it is the raw x branch of in_proj; the kernel forms the
+ *           window [conv_in, xin], applies the depthwise filter conv_w (ED, K) + conv_b (ED)
+ *           and SiLU, and writes the shifted window to conv_out (B, ED, K-1).
+ *   delta : (B, ED) activations; MB200_DELTA_SOFTPLUS applies softplus(delta + delta_bias).
+ *   Bm, Cm: (B, N) activations.  z: (B, ED) or NULL.  h_in: (B, ED, N) float32 or NULL (= 0).
+ *   h_out : (B, ED, N) float32 (may alias h_in).  y: (B, ED).
+ * Note: when conv_w != NULL, delta/Bm/Cm depend on the post-conv x through x_proj, so the
+ * host runs `mb200_conv_step` first; the combined form exists for callers that pass
+ * projections computed from the value this function also returns in xc_out. */
+int mb200_ssm_step(const void* x, const void* delta, const void* z,
+                   const float* A, const void* Bm, const void* Cm, const float* D,
+                   const float* delta_bias, const float* h_in, float* h_out, void* y,
+                   int64_t B, int64_t ED, int N,
+                   int64_t x_sb, int64_t d_sb, int64_t z_sb, int64_t b_sb, int64_t c_sb,
+                   int64_t y_sb, int dtype, int flags, void* stream);
+
+/* ---- Conv-window step of MambaBlock.step (mambapy/mamba.py:366-369 and :379):
+ *   xc[b,e]        = silu( sum_k w[e,k]*win[b,e,k] + bias[e] ),  win = [conv_in[b,e,:], xin[b,e]]
+ *   conv_out[b,e,:] = win[b,e,1:]
+ * xin: (B, ED) activations (row stride x_sb); conv_in/conv_out: (B, ED, K-1) dense, same
+ * dtype; w: (ED, K) float32 dense; bias: (ED) float32 or NULL; xc: (B, ED) dense.  K <= 8. */
+int mb200_conv_step(const void* xin, const void* conv_in, const float* w, const float* bias,
+                    void* xc, void* conv_out,
+                    int64_t B, int64_t ED, int K, int64_t x_sb, int dtype, void* stream);
+
+/* ---- Sequence-sharded scan: fold the per-shard carries after they were all-gathered.
+ * No reference counterpart (the reference is single-device); the single-device answer on
+ * the concatenated sequence is what it must reproduce.
+ *   P, S : (R, M) float32 — per shard r the decay product over the shard and the state the
+ *          shard reaches from a zero start, M = B*ED*N.
+ *   reverse == 0: out[m] = state entering shard `rank`  = fold of shards 0..rank-1 in order
+ *                 (h <- P_q*h + S_q), starting from 0.
+ *   reverse == 1: out[m] = gradient carry entering shard `rank` from the right = fold of
+ *                 shards R-1..rank+1 (g <- S_q + P_q*g), starting from 0. */
+int mb200_carry_fold(const float* P, const float* S, float* out,
+                     int64_t R, int64_t M, int rank, int reverse, void* stream);
+
+/* ---- Decay product of a shard: P[b,e,n] = exp(A[e,n] * sum_t delta[b,t,e]) (with the same
+ * softplus option as the scan).  Used with mb200_carry_fold by the sequence-sharded scan. */
+int mb200_decay_prod(const void* delta, const float* A, const float* delta_bias, float* P,
+                     int64_t B, int64_t L, int64_t ED, int N,
+                     int64_t d_sb, int64_t d_sl, int dtype, int flags, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MAMBA_B200_H */

@@ -1,0 +1,93 @@
+// Shared device helpers for the selective-scan kernels (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "mamba_b200.h"
+
+namespace mb200 {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+// ---- element <-> float conversion -------------------------------------------------
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static constexpr int kVec = 4;                       // elements per 16-byte vector
+  __device__ static float to_f(float v) { return v; }
+  __device__ static float from_f(float v) { return v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static constexpr int kVec = 8;
+  __device__ static float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+  __device__ static __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
+};
+
+// A 16-byte vector of T, loaded / stored with one 128-bit access.
+template <typename T> struct alignas(16) Vec16 {
+  T v[Elem<T>::kVec];
+};
+
+template <typename T>
+__device__ __forceinline__ Vec16<T> ldg16(const T* p) {
+  Vec16<T> r;
+  *reinterpret_cast<uint4*>(&r) = __ldg(reinterpret_cast<const uint4*>(p));
+  return r;
+}
+// streaming variants: data touched exactly once should not displace reusable lines
+template <typename T>
+__device__ __forceinline__ Vec16<T> ldcs16(const T* p) {
+  Vec16<T> r;
+  *reinterpret_cast<uint4*>(&r) = __ldcs(reinterpret_cast<const uint4*>(p));
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ void stcs16(T* p, const Vec16<T>& r) {
+  __stcs(reinterpret_cast<uint4*>(p), *reinterpret_cast<const uint4*>(&r));
+}
+
+__host__ __device__ __forceinline__ int64_t min64(int64_t a, int64_t b) { return a < b ? a : b; }
+
+// ---- math ---------------------------------------------------------------------------
+__device__ __forceinline__ float ex2f(float x) {       // 2^x on the MUFU pipe
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float softplusf(float x) {   // torch semantics: threshold 20
+  return x > 20.f ? x : log1pf(__expf(x));
+}
+__device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(-x)); }
+
+// ---- packed float2 arithmetic (one issue slot for two lanes of FMA work) ------------
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{.reg .b64 ra, rb, rc, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "mov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+      "mov.b64 {%0, %1}, rd;}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{.reg .b64 ra, rb, rd;\n\t"
+      "mov.b64 ra, {%2, %3};\n\t"
+      "mov.b64 rb, {%4, %5};\n\t"
+      "mul.rn.f32x2 rd, ra, rb;\n\t"
+      "mov.b64 {%0, %1}, rd;}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
+// ---- host-side helpers ----------------------------------------------------------------
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+inline int check_launch() {
+  return cudaGetLastError() == cudaSuccess ? MB200_OK : MB200_ELAUNCH;
+}
+
+}  // namespace mb200

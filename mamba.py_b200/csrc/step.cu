@@ -1,0 +1,249 @@
+// Single-token decode kernels: the SSM state update of MambaBlock.ssm_step and the
+// conv-window update of MambaBlock.step.  Both are pure streaming work: the (B, ED, N)
+// float32 state is read once and written once per layer-step, which is what bounds them.
+//
+// Mapping for the state update: N/4 lanes share a channel, each lane moves one float4 of the
+// state (so a warp reads 512 contiguous bytes of h), computes its four decays and partial
+// C-contraction, and the lanes of a channel combine with warp shuffles.
+#include "common.cuh"
+
+namespace mb200 {
+namespace {
+
+constexpr int kStepThreads = 256;
+
+template <typename T, int N>
+__global__ void __launch_bounds__(kStepThreads)
+ssm_step_kernel(const T* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ z,
+                const float* __restrict__ A, const T* __restrict__ Bm, const T* __restrict__ Cm,
+                const float* __restrict__ D, const float* __restrict__ delta_bias,
+                const float* __restrict__ h_in, float* __restrict__ h_out, T* __restrict__ y,
+                int64_t ED, int64_t x_sb, int64_t d_sb, int64_t z_sb, int64_t b_sb,
+                int64_t c_sb, int64_t y_sb, int flags) {
+  constexpr int kLPE = N / 4;
+  constexpr int kEPB = kStepThreads / kLPE;          // channels per CTA
+  const int tid = threadIdx.x;
+  const int q = tid % kLPE;
+  const int64_t e = int64_t(blockIdx.x) * kEPB + tid / kLPE;
+  const int64_t b = blockIdx.y;
+  const bool ok = e < ED;
+  float yv = 0.f, xv = 0.f;
+  if (ok) {
+    xv = Elem<T>::to_f(x[b * x_sb + e]);
+    float dv = Elem<T>::to_f(delta[b * d_sb + e]);
+    if (flags & MB200_DELTA_SOFTPLUS) dv = softplusf(dv + delta_bias[e]);
+    const float4 Av = *reinterpret_cast<const float4*>(A + e * N + 4 * q);
+    float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (h_in) hv = __ldcs(reinterpret_cast<const float4*>(h_in + (b * ED + e) * N + 4 * q));
+    const float a4[4] = {Av.x, Av.y, Av.z, Av.w};
+    float h4[4] = {hv.x, hv.y, hv.z, hv.w};
+    const float dx = dv * xv;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = ex2f(dv * a4[j] * kLog2e);
+      const float bj = Elem<T>::to_f(Bm[b * b_sb + 4 * q + j]);
+      const float cj = Elem<T>::to_f(Cm[b * c_sb + 4 * q + j]);
+      h4[j] = fmaf(a, h4[j], dx * bj);
+      yv = fmaf(h4[j], cj, yv);
+    }
+    __stcs(reinterpret_cast<float4*>(h_out + (b * ED + e) * N + 4 * q),
+           make_float4(h4[0], h4[1], h4[2], h4[3]));
+  }
+#pragma unroll
+  for (int s = kLPE / 2; s >= 1; s >>= 1) yv += __shfl_xor_sync(0xffffffffu, yv, s);
+  if (ok && q == 0) {
+    yv = fmaf(D ? D[e] : 0.f, xv, yv);
+    if (z) {
+      const float zv = Elem<T>::to_f(z[b * z_sb + e]);
+      yv *= zv * sigmoidf(zv);
+    }
+    y[b * y_sb + e] = Elem<T>::from_f(yv);
+  }
+}
+
+// xc = silu(sum_k w[e,k]*win[k] + bias[e]) with win = [conv_in[b,e,:], xin[b,e]]; conv_out = win[1:].
+template <typename T>
+__global__ void conv_step_kernel(const T* __restrict__ xin, const T* __restrict__ conv_in,
+                                 const float* __restrict__ w, const float* __restrict__ bias,
+                                 T* __restrict__ xc, T* __restrict__ conv_out,
+                                 int64_t ED, int K, int64_t x_sb) {
+  const int64_t e = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t b = blockIdx.y;
+  if (e >= ED) return;
+  const T* ci = conv_in + (b * ED + e) * (K - 1);
+  T* co = conv_out + (b * ED + e) * (K - 1);
+  const float xn = Elem<T>::to_f(xin[b * x_sb + e]);
+  float acc = bias ? bias[e] : 0.f;
+  float win[8];
+  for (int k = 0; k < K - 1; ++k) win[k] = Elem<T>::to_f(ci[k]);
+  win[K - 1] = xn;
+  for (int k = 0; k < K; ++k) acc = fmaf(w[e * K + k], win[k], acc);
+  for (int k = 0; k < K - 1; ++k) co[k] = Elem<T>::from_f(win[k + 1]);
+  xc[b * ED + e] = Elem<T>::from_f(acc * sigmoidf(acc));
+}
+
+// Fold of all-gathered shard carries (see mamba_b200.h).
+__global__ void carry_fold_kernel(const float* __restrict__ P, const float* __restrict__ S,
+                                  float* __restrict__ out, int64_t R, int64_t M, int rank,
+                                  int reverse) {
+  const int64_t m = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (m >= M) return;
+  float cur = 0.f;
+  if (!reverse) {
+    for (int64_t r = 0; r < rank; ++r) cur = fmaf(P[r * M + m], cur, S[r * M + m]);
+  } else {
+    for (int64_t r = R - 1; r > rank; --r) cur = fmaf(P[r * M + m], cur, S[r * M + m]);
+  }
+  out[m] = cur;
+}
+
+// P[b,e,n] = exp(A[e,n] * sum_t delta[b,t,e]); a CTA column-sums a strip of 32 channels.
+template <typename T>
+__global__ void decay_prod_kernel(const T* __restrict__ delta, const float* __restrict__ A,
+                                  const float* __restrict__ delta_bias, float* __restrict__ P,
+                                  int64_t L, int64_t ED, int N, int64_t d_sb, int64_t d_sl,
+                                  int flags) {
+  __shared__ float part[8][33];
+  const int lx = threadIdx.x, ly = threadIdx.y;              // 32 x 8
+  const int64_t e = int64_t(blockIdx.x) * 32 + lx;
+  const int64_t b = blockIdx.y;
+  // Kahan-compensated column sum: L can be 10^5 and the sum feeds an exponent
+  float s = 0.f, comp = 0.f;
+  if (e < ED) {
+    const float bias = (flags & MB200_DELTA_SOFTPLUS) ? delta_bias[e] : 0.f;
+    for (int64_t t = ly; t < L; t += 8) {
+      float dv = Elem<T>::to_f(delta[b * d_sb + t * d_sl + e]);
+      if (flags & MB200_DELTA_SOFTPLUS) dv = softplusf(dv + bias);
+      const float yk = dv - comp;
+      const float tk = s + yk;
+      comp = (tk - s) - yk;
+      s = tk;
+    }
+  }
+  part[ly][lx] = s;
+  __syncthreads();
+  if (ly == 0 && e < ED) {
+    float tot = 0.f;
+    for (int k = 0; k < 8; ++k) tot += part[k][lx];
+    for (int n = 0; n < N; ++n) P[(b * ED + e) * N + n] = ex2f(tot * A[e * N + n] * kLog2e);
+  }
+}
+
+}  // namespace
+}  // namespace mb200
+
+using namespace mb200;
+
+template <typename T>
+static int ssm_step_t(const void* x, const void* delta, const void* z, const float* A,
+                      const void* Bm, const void* Cm, const float* D, const float* delta_bias,
+                      const float* h_in, float* h_out, void* y, int64_t B, int64_t ED, int N,
+                      int64_t x_sb, int64_t d_sb, int64_t z_sb, int64_t b_sb, int64_t c_sb,
+                      int64_t y_sb, int flags, cudaStream_t st) {
+#define MB200_STEP(NN)                                                                          \
+  {                                                                                             \
+    constexpr int epb = kStepThreads / (NN / 4);                                                \
+    dim3 grid(unsigned((ED + epb - 1) / epb), unsigned(B));                                     \
+    ssm_step_kernel<T, NN><<<grid, kStepThreads, 0, st>>>(                                      \
+        (const T*)x, (const T*)delta, (const T*)z, A, (const T*)Bm, (const T*)Cm, D, delta_bias, \
+        h_in, h_out, (T*)y, ED, x_sb, d_sb, z_sb, b_sb, c_sb, y_sb, flags);                     \
+    return check_launch();                                                                      \
+  }
+  switch (N) {
+    case 8: MB200_STEP(8)
+    case 16: MB200_STEP(16)
+    case 32: MB200_STEP(32)
+    case 64: MB200_STEP(64)
+    default: return MB200_ENSTATE;
+  }
+#undef MB200_STEP
+}
+
+extern "C" int mb200_ssm_step(const void* x, const void* delta, const void* z, const float* A,
+                              const void* Bm, const void* Cm, const float* D,
+                              const float* delta_bias, const float* h_in, float* h_out, void* y,
+                              int64_t B, int64_t ED, int N, int64_t x_sb, int64_t d_sb,
+                              int64_t z_sb, int64_t b_sb, int64_t c_sb, int64_t y_sb, int dtype,
+                              int flags, void* stream) {
+  if (B < 0 || ED < 0) return MB200_EINVAL;
+  if (dtype != MB200_F32 && dtype != MB200_BF16) return MB200_EDTYPE;
+  if (N != 8 && N != 16 && N != 32 && N != 64) return MB200_ENSTATE;
+  if (B == 0 || ED == 0) return MB200_OK;
+  if (!x || !delta || !A || !Bm || !Cm || !h_out || !y) return MB200_EINVAL;
+  if ((flags & MB200_DELTA_SOFTPLUS) && !delta_bias) return MB200_EINVAL;
+  if (B > 65535) return MB200_ETOOBIG;
+  if (!aligned16(h_in) || !aligned16(h_out) || !aligned16(A)) return MB200_EALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return dtype == MB200_F32
+             ? ssm_step_t<float>(x, delta, z, A, Bm, Cm, D, delta_bias, h_in, h_out, y, B, ED, N,
+                                 x_sb, d_sb, z_sb, b_sb, c_sb, y_sb, flags, st)
+             : ssm_step_t<__nv_bfloat16>(x, delta, z, A, Bm, Cm, D, delta_bias, h_in, h_out, y, B,
+                                         ED, N, x_sb, d_sb, z_sb, b_sb, c_sb, y_sb, flags, st);
+}
+
+extern "C" int mb200_conv_step(const void* xin, const void* conv_in, const float* w,
+                               const float* bias, void* xc, void* conv_out, int64_t B, int64_t ED,
+                               int K, int64_t x_sb, int dtype, void* stream) {
+  if (B < 0 || ED < 0 || K < 1) return MB200_EINVAL;
+  if (K > 8) return MB200_ETOOBIG;
+  if (dtype != MB200_F32 && dtype != MB200_BF16) return MB200_EDTYPE;
+  if (B == 0 || ED == 0) return MB200_OK;
+  if (!xin || !w || !xc || (K > 1 && (!conv_in || !conv_out))) return MB200_EINVAL;
+  if (B > 65535) return MB200_ETOOBIG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(unsigned((ED + 255) / 256), unsigned(B));
+  if (dtype == MB200_F32)
+    conv_step_kernel<float><<<grid, 256, 0, st>>>((const float*)xin, (const float*)conv_in, w, bias,
+                                                  (float*)xc, (float*)conv_out, ED, K, x_sb);
+  else
+    conv_step_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+        (const __nv_bfloat16*)xin, (const __nv_bfloat16*)conv_in, w, bias, (__nv_bfloat16*)xc,
+        (__nv_bfloat16*)conv_out, ED, K, x_sb);
+  return check_launch();
+}
+
+extern "C" int mb200_carry_fold(const float* P, const float* S, float* out, int64_t R, int64_t M,
+                                int rank, int reverse, void* stream) {
+  if (R < 1 || M < 0 || rank < 0 || rank >= R) return MB200_EINVAL;
+  if (M == 0) return MB200_OK;
+  if (!P || !S || !out) return MB200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  carry_fold_kernel<<<unsigned((M + 255) / 256), 256, 0, st>>>(P, S, out, R, M, rank, reverse);
+  return check_launch();
+}
+
+extern "C" int mb200_decay_prod(const void* delta, const float* A, const float* delta_bias,
+                                float* P, int64_t B, int64_t L, int64_t ED, int N, int64_t d_sb,
+                                int64_t d_sl, int dtype, int flags, void* stream) {
+  if (B < 0 || L < 0 || ED < 0 || N < 1) return MB200_EINVAL;
+  if (dtype != MB200_F32 && dtype != MB200_BF16) return MB200_EDTYPE;
+  if (B == 0 || ED == 0) return MB200_OK;
+  if (!A || !P || (L > 0 && !delta)) return MB200_EINVAL;
+  if ((flags & MB200_DELTA_SOFTPLUS) && !delta_bias) return MB200_EINVAL;
+  if (B > 65535) return MB200_ETOOBIG;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(unsigned((ED + 31) / 32), unsigned(B)), block(32, 8);
+  if (dtype == MB200_F32)
+    decay_prod_kernel<float><<<grid, block, 0, st>>>((const float*)delta, A, delta_bias, P, L, ED, N,
+                                                     d_sb, d_sl, flags);
+  else
+    decay_prod_kernel<__nv_bfloat16><<<grid, block, 0, st>>>((const __nv_bfloat16*)delta, A,
+                                                             delta_bias, P, L, ED, N, d_sb, d_sl, flags);
+  return check_launch();
+}
+
+extern "C" const char* mb200_strerror(int code) {
+  switch (code) {
+    case MB200_OK: return "ok";
+    case MB200_EINVAL: return "invalid argument (shape, size or missing pointer)";
+    case MB200_EDTYPE: return "unsupported dtype code";
+    case MB200_ENSTATE: return "d_state must be 8, 16, 32 or 64";
+    case MB200_EALIGN: return "a float32 state/carry pointer is not 16-byte aligned";
+    case MB200_ELAUNCH: return "CUDA kernel launch failed";
+    case MB200_ETOOBIG: return "size exceeds a limit of this entry point";
+    case MB200_ESETUP: return "per-device set-up failed";
+    default: return "unknown error";
+  }
+}
+
+extern "C" int mb200_version(void) { return 100; }

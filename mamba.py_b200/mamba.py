@@ -1,0 +1,275 @@
+"""Drop-ins for the scan methods of the reference's MambaBlock (mambapy/mamba.py).
+
+The functions below take `self` first so they can be bound onto the reference's MambaBlock
+(see `mamba_b200.install`) or onto any object with the same attribute names:
+
+    selective_scan(self, x, delta, A, B, C, D)      mambapy/mamba.py:274-295
+    selective_scan_seq(self, x, delta, A, B, C, D)  mambapy/mamba.py:297-327 (same kernel)
+    ssm_step(self, x, h)                            mambapy/mamba.py:384-414
+    step(self, x, cache)                            mambapy/mamba.py:351-382
+    ssm(self, x, z) / forward(self, x)              mambapy/mamba.py:236-272 / :205-234 with the
+                                                    softplus, the scan and the gate in one kernel
+
+`selective_scan_fn` is the functional form with the optional gate `z`, the fused
+`softplus(delta + delta_bias)`, an incoming state `h0` and the outgoing state.
+Everything runs in libmamba_b200.so on CUDA tensors; there is no CPU path.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("mamba_b200 runs on CUDA tensors only (there is no CPU path)")
+
+
+def _rows(t: torch.Tensor | None, dtype) -> torch.Tensor | None:
+    """Cast to the activation dtype and make the last dim unit-stride (copy only if needed)."""
+    if t is None:
+        return None
+    if t.dtype != dtype:
+        t = t.to(dtype)
+    if t.stride(-1) != 1:
+        t = t.contiguous()
+    return t
+
+
+def _act_dtype(x: torch.Tensor):
+    if x.dtype in (torch.float32, torch.bfloat16):
+        return x.dtype
+    raise TypeError(f"mamba_b200 kernels take float32 or bfloat16 activations, got {x.dtype}")
+
+
+def _f32(t):
+    return None if t is None else t.detach().float().contiguous()
+
+
+def sscan_fwd_raw(x, delta, A, Bm, Cm, D, z=None, delta_bias=None, h0=None,
+                  want_last=False, want_carries=False, want_y=True):
+    """Launch the fused forward.  Tensors must already be prepared by the caller.
+
+    Returns (y, hT, carries); entries not asked for are None."""
+    lib = _lib.load()
+    Bsz, L, ED = x.shape
+    N = A.shape[1]
+    dev = x.device
+    y = torch.empty((Bsz, L, ED), dtype=x.dtype, device=dev) if want_y else None
+    hT = torch.empty((Bsz, ED, N), dtype=torch.float32, device=dev) if want_last else None
+    chunk = lib.mb200_sscan_chunk()
+    carries = (torch.empty((Bsz, (L + chunk - 1) // chunk, ED, N), dtype=torch.float32, device=dev)
+               if want_carries else None)
+    flags = _lib.DELTA_SOFTPLUS if delta_bias is not None else 0
+    zs = (z.stride(0), z.stride(1)) if z is not None else (0, 0)
+    ys = (y.stride(0), y.stride(1)) if y is not None else (0, 0)
+    with torch.cuda.device(dev):
+        rc = lib.mb200_sscan_fwd(
+            x.data_ptr(), delta.data_ptr(), _lib.ptr(z), A.data_ptr(), Bm.data_ptr(), Cm.data_ptr(),
+            _lib.ptr(D), _lib.ptr(delta_bias), _lib.ptr(h0), _lib.ptr(y), _lib.ptr(hT),
+            _lib.ptr(carries), Bsz, L, ED, N,
+            x.stride(0), x.stride(1), delta.stride(0), delta.stride(1), zs[0], zs[1],
+            Bm.stride(0), Bm.stride(1), Cm.stride(0), Cm.stride(1), ys[0], ys[1],
+            _lib.dtype_code(x.dtype), flags, _lib.current_stream(dev))
+    _lib.check(rc, "mb200_sscan_fwd")
+    return y, hT, carries
+
+
+def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None, want_g_out=False):
+    """Launch the fused backward.  Returns (dx, ddelta, dz, dB, dC, dA, dD, dbias, g_out)."""
+    lib = _lib.load()
+    Bsz, L, ED = x.shape
+    N = A.shape[1]
+    dev = x.device
+    dx = torch.empty((Bsz, L, ED), dtype=x.dtype, device=dev)
+    dd = torch.empty_like(dx)
+    dz = torch.empty_like(dx) if z is not None else None
+    dB = torch.zeros((Bsz, L, N), dtype=torch.float32, device=dev)
+    dC = torch.zeros_like(dB)
+    dA = torch.zeros((ED, N), dtype=torch.float32, device=dev)
+    dD = torch.zeros((ED,), dtype=torch.float32, device=dev)
+    dbias = torch.zeros((ED,), dtype=torch.float32, device=dev) if delta_bias is not None else None
+    g_out = torch.empty((Bsz, ED, N), dtype=torch.float32, device=dev) if want_g_out else None
+    flags = _lib.DELTA_SOFTPLUS if delta_bias is not None else 0
+    zs = (z.stride(0), z.stride(1)) if z is not None else (0, 0)
+    dzs = (dz.stride(0), dz.stride(1)) if dz is not None else (0, 0)
+    with torch.cuda.device(dev):
+        rc = lib.mb200_sscan_bwd(
+            x.data_ptr(), delta.data_ptr(), _lib.ptr(z), A.data_ptr(), Bm.data_ptr(), Cm.data_ptr(),
+            _lib.ptr(D), _lib.ptr(delta_bias), dy.data_ptr(), carries.data_ptr(), _lib.ptr(g_in),
+            dx.data_ptr(), dd.data_ptr(), _lib.ptr(dz), dB.data_ptr(), dC.data_ptr(), dA.data_ptr(),
+            dD.data_ptr(), _lib.ptr(dbias), _lib.ptr(g_out), Bsz, L, ED, N,
+            x.stride(0), x.stride(1), delta.stride(0), delta.stride(1), zs[0], zs[1],
+            Bm.stride(0), Bm.stride(1), Cm.stride(0), Cm.stride(1), dy.stride(0), dy.stride(1),
+            dx.stride(0), dx.stride(1), dd.stride(0), dd.stride(1), dzs[0], dzs[1],
+            _lib.dtype_code(x.dtype), flags, _lib.current_stream(dev))
+    _lib.check(rc, "mb200_sscan_bwd")
+    return dx, dd, dz, dB, dC, dA, dD, dbias, g_out
+
+
+class SelectiveScanFn(torch.autograd.Function):
+    """y (and optionally the last state) of the fused scan; gradients for every input."""
+
+    @staticmethod
+    def forward(ctx, x, delta, A, Bm, Cm, D, z, delta_bias, h0, return_last_state):
+        _require_cuda(x, delta, A, Bm, Cm, D, z, delta_bias, h0)
+        dt = _act_dtype(x)
+        xs, ds, zs = _rows(x, dt), _rows(delta, dt), _rows(z, dt)
+        Bs, Cs = _rows(Bm, dt), _rows(Cm, dt)
+        A32, D32, b32, h032 = _f32(A), _f32(D), _f32(delta_bias), _f32(h0)
+        needs_grad = any(t is not None and t.requires_grad
+                         for t in (x, delta, A, Bm, Cm, D, z, delta_bias, h0))
+        y, hT, carries = sscan_fwd_raw(xs, ds, A32, Bs, Cs, D32, zs, b32, h032,
+                                       want_last=return_last_state, want_carries=needs_grad)
+        ctx.save_for_backward(xs, ds, A32, Bs, Cs, D32, zs, b32, carries)
+        ctx.in_dtypes = tuple(None if t is None else t.dtype
+                              for t in (x, delta, A, Bm, Cm, D, z, delta_bias, h0))
+        ctx.has_h0 = h0 is not None
+        if return_last_state:
+            ctx.mark_non_differentiable(hT)
+            return y, hT
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, *unused):
+        xs, ds, A32, Bs, Cs, D32, zs, b32, carries = ctx.saved_tensors
+        dy = _rows(dy, xs.dtype)
+        dx, dd, dz, dB, dC, dA, dD, dbias, g_out = sscan_bwd_raw(
+            xs, ds, A32, Bs, Cs, D32, zs, b32, dy, carries, want_g_out=ctx.has_h0)
+        tx, td, tA, tB, tC, tD, tz, tb, th = ctx.in_dtypes
+        cast = lambda g, t: None if (g is None or t is None) else g.to(t)
+        return (cast(dx, tx), cast(dd, td), cast(dA, tA), cast(dB, tB), cast(dC, tC),
+                cast(dD, tD), cast(dz, tz), cast(dbias, tb), cast(g_out, th), None)
+
+
+def selective_scan_fn(x, delta, A, B, C, D=None, z=None, delta_bias=None, h0=None,
+                      return_last_state=False):
+    """Fused selective scan.
+
+    x, delta, z : (B, L, ED)   B, C : (B, L, N)   A : (ED, N)   D : (ED)
+    With `delta_bias` the kernel applies delta = softplus(delta + delta_bias) itself (the
+    contract of the fused seam at mambapy/mamba.py:260); with `z` it also applies the
+    y * silu(z) gate (mambapy/mamba.py:229-231).  Returns y (B, L, ED), plus the final state
+    (B, ED, N) float32 when `return_last_state`.
+    """
+    return SelectiveScanFn.apply(x, delta, A, B, C, D, z, delta_bias, h0, return_last_state)
+
+
+# ----------------------------------------------------------------- MambaBlock method drop-ins
+
+def selective_scan(self, x, delta, A, B, C, D):
+    """mambapy/mamba.py:274-295.  x, delta: (B, L, ED); A: (ED, N); B, C: (B, L, N); D: (ED)."""
+    return selective_scan_fn(x, delta, A, B, C, D)
+
+
+def selective_scan_seq(self, x, delta, A, B, C, D):
+    """mambapy/mamba.py:297-327.  The sequential variant computes the same y; same kernel."""
+    return selective_scan_fn(x, delta, A, B, C, D)
+
+
+def ssm_step_fn(x, h, delta, A, B, C, D=None, z=None, delta_bias=None):
+    """One decode step on projected inputs.  x, delta, z: (B, ED); B, C: (B, N); h: (B, ED, N) or None.
+
+    Returns (y, h_new); h_new is a fresh float32 tensor (the reference also returns a new one,
+    mambapy/mamba.py:408)."""
+    _require_cuda(x, delta, A, B, C, D, z, delta_bias, h)
+    lib = _lib.load()
+    dt = _act_dtype(x)
+    xs, ds, zs, Bs, Cs = (_rows(t, dt) for t in (x, delta, z, B, C))
+    A32, D32, b32 = _f32(A), _f32(D), _f32(delta_bias)
+    h32 = None if h is None else h.float().contiguous()
+    Bsz, ED = xs.shape
+    N = A32.shape[1]
+    h_new = torch.empty((Bsz, ED, N), dtype=torch.float32, device=xs.device)
+    y = torch.empty((Bsz, ED), dtype=dt, device=xs.device)
+    flags = _lib.DELTA_SOFTPLUS if b32 is not None else 0
+    with torch.cuda.device(xs.device):
+        rc = lib.mb200_ssm_step(
+            xs.data_ptr(), ds.data_ptr(), _lib.ptr(zs), A32.data_ptr(), Bs.data_ptr(), Cs.data_ptr(),
+            _lib.ptr(D32), _lib.ptr(b32), _lib.ptr(h32), h_new.data_ptr(), y.data_ptr(), Bsz, ED, N,
+            xs.stride(0), ds.stride(0), zs.stride(0) if zs is not None else 0, Bs.stride(0),
+            Cs.stride(0), y.stride(0), _lib.dtype_code(dt), flags, _lib.current_stream(xs.device))
+    _lib.check(rc, "mb200_ssm_step")
+    return y, h_new
+
+
+def conv_step_fn(x, inputs, weight, bias):
+    """Conv-window part of a decode step (mambapy/mamba.py:366-369, :379).
+
+    x: (B, ED) new pre-conv input; inputs: (B, ED, d_conv-1) cached window;
+    weight: (ED, 1, d_conv) depthwise filter; bias: (ED) or None.
+    Returns (silu(conv(x)), new window)."""
+    _require_cuda(x, inputs, weight, bias)
+    lib = _lib.load()
+    dt = _act_dtype(x)
+    xs = _rows(x, dt)
+    win = inputs.to(dt).contiguous()
+    Bsz, ED = xs.shape
+    K = weight.shape[-1]
+    w32 = weight.detach().reshape(ED, K).float().contiguous()
+    b32 = _f32(bias)
+    xc = torch.empty((Bsz, ED), dtype=dt, device=xs.device)
+    new_win = torch.empty_like(win)
+    with torch.cuda.device(xs.device):
+        rc = lib.mb200_conv_step(xs.data_ptr(), win.data_ptr(), w32.data_ptr(), _lib.ptr(b32),
+                                 xc.data_ptr(), new_win.data_ptr(), Bsz, ED, K, xs.stride(0),
+                                 _lib.dtype_code(dt), _lib.current_stream(xs.device))
+    _lib.check(rc, "mb200_conv_step")
+    return xc, new_win
+
+
+def _project(self, x):
+    """delta (pre-softplus, without bias), B, C from x as in mambapy/mamba.py:393-396."""
+    cfg = self.config
+    deltaBC = self.x_proj(x)
+    delta, B, C = torch.split(deltaBC, [cfg.dt_rank, cfg.d_state, cfg.d_state], dim=-1)
+    delta, B, C = self._apply_layernorms(delta, B, C)
+    return delta, B, C
+
+
+def ssm_step(self, x, h):
+    """mambapy/mamba.py:384-414.  x: (B, ED); h: (B, ED, N) or None.  Returns (y, h)."""
+    A = -torch.exp(self.A_log.float())
+    delta, B, C = _project(self, x)
+    delta = F.linear(delta, self.dt_proj.weight)          # bias and softplus happen in the kernel
+    return ssm_step_fn(x, h, delta, A, B, C, self.D, delta_bias=self.dt_proj.bias)
+
+
+def step(self, x, cache):
+    """mambapy/mamba.py:351-382.  x: (B, D); cache = (h (B, ED, N) or None, inputs (B, ED, d_conv-1)).
+
+    Returns (output (B, D), (h, inputs)) with fresh cache tensors."""
+    h, inputs = cache
+    xz = self.in_proj(x)
+    xs, z = xz.chunk(2, dim=1)
+    xc, inputs = conv_step_fn(xs, inputs, self.conv1d.weight, self.conv1d.bias)
+    A = -torch.exp(self.A_log.float())
+    delta, B, C = _project(self, xc)
+    delta = F.linear(delta, self.dt_proj.weight)
+    y, h = ssm_step_fn(xc, h, delta, A, B, C, self.D, z=z, delta_bias=self.dt_proj.bias)
+    return self.out_proj(y), (h, inputs)
+
+
+def ssm(self, x, z):
+    """mambapy/mamba.py:236-272 with softplus(delta + dt_bias), the scan and the gate fused.
+
+    Like the reference's own fused branch (mambapy/mamba.py:252-261) this returns the GATED y,
+    so the matching `forward` below skips the z branch."""
+    A = -torch.exp(self.A_log.float())
+    delta, B, C = _project(self, x)
+    delta = F.linear(delta, self.dt_proj.weight)          # (B, L, ED), no transposes needed
+    return selective_scan_fn(x, delta, A, B, C, self.D, z=z, delta_bias=self.dt_proj.bias)
+
+
+def forward(self, x):
+    """mambapy/mamba.py:205-234 with the scan path fused; x: (B, L, D) -> (B, L, D)."""
+    _, L, _ = x.shape
+    xz = self.in_proj(x)
+    xs, z = xz.chunk(2, dim=-1)
+    xs = self.conv1d(xs.transpose(1, 2))[:, :, :L].transpose(1, 2)
+    xs = F.silu(xs)
+    y = ssm(self, xs, z)
+    return self.out_proj(y)

@@ -1,0 +1,70 @@
+"""install() / uninstall(): rebind the reference's scan entry points to the CUDA kernels.
+
+The reference has no plugin registry; its seams are Python names.  `pscan` is imported BY NAME
+into mambapy.mamba, mambapy.vim and mambapy.onnx.mamba_onnx (mambapy/mamba.py:9), so replacing
+mambapy.pscan.pscan alone would not reach them; every importer is rebound, and the MambaBlock
+methods of the scan path are replaced.  Nothing is added to any module's parameters or
+buffers, so reference state_dicts keep loading unchanged.
+"""
+from __future__ import annotations
+
+import importlib
+import sys
+
+from . import mamba as _m
+from . import pscan as _p
+
+_saved: list[tuple[object, str, object]] = []
+
+_PSCAN_IMPORTERS = ("mambapy.mamba", "mambapy.vim", "mambapy.onnx.mamba_onnx", "mambapy.jamba")
+_BLOCK_METHODS = ("selective_scan", "selective_scan_seq", "ssm_step", "step")
+
+
+def _swap(obj, name, new):
+    _saved.append((obj, name, getattr(obj, name)))
+    setattr(obj, name, new)
+
+
+def installed() -> bool:
+    return bool(_saved)
+
+
+def install(fuse_block: bool = False) -> None:
+    """Patch an importable `mambapy`.
+
+    fuse_block=False keeps MambaBlock.forward/ssm as they are and swaps only the methods whose
+    signatures the reference defines (selective_scan, selective_scan_seq, ssm_step, step) plus
+    pscan/PScan.  fuse_block=True also swaps MambaBlock.ssm and MambaBlock.forward for the
+    variants that run softplus, scan and gate in one kernel.
+    """
+    if _saved:
+        return
+    ref_pscan = importlib.import_module("mambapy.pscan")
+    _swap(ref_pscan, "pscan", _p.pscan)
+    _swap(ref_pscan, "PScan", _p.PScan)
+    for modname in _PSCAN_IMPORTERS:
+        mod = sys.modules.get(modname)
+        if mod is None and modname == "mambapy.mamba":
+            mod = importlib.import_module(modname)
+        if mod is not None and hasattr(mod, "pscan"):
+            _swap(mod, "pscan", _p.pscan)
+    blocks = [sys.modules["mambapy.mamba"].MambaBlock]
+    for modname in ("mambapy.vim", "mambapy.onnx.mamba_onnx"):
+        mod = sys.modules.get(modname)
+        if mod is not None and hasattr(mod, "MambaBlock"):
+            blocks.append(mod.MambaBlock)
+    for i, blk in enumerate(blocks):
+        for name in _BLOCK_METHODS:
+            # the ONNX variant's step() has another signature; only same-signature methods move
+            if hasattr(blk, name) and (i == 0 or name in ("selective_scan", "selective_scan_seq")):
+                _swap(blk, name, getattr(_m, name))
+    if fuse_block:
+        _swap(blocks[0], "ssm", _m.ssm)
+        _swap(blocks[0], "forward", _m.forward)
+
+
+def uninstall() -> None:
+    """Undo install(); the reference's own code runs again."""
+    while _saved:
+        obj, name, old = _saved.pop()
+        setattr(obj, name, old)
