@@ -12,7 +12,7 @@ import importlib
 import sys
 
 from . import mamba as _m
-from . import pscan as _p
+from .pscan import PScan as _PScan, pscan as _pscan
 
 _saved: list[tuple[object, str, object]] = []
 
@@ -40,14 +40,14 @@ def install(fuse_block: bool = False) -> None:
     if _saved:
         return
     ref_pscan = importlib.import_module("mambapy.pscan")
-    _swap(ref_pscan, "pscan", _p.pscan)
-    _swap(ref_pscan, "PScan", _p.PScan)
+    _swap(ref_pscan, "pscan", _pscan)
+    _swap(ref_pscan, "PScan", _PScan)
     for modname in _PSCAN_IMPORTERS:
         mod = sys.modules.get(modname)
         if mod is None and modname == "mambapy.mamba":
             mod = importlib.import_module(modname)
         if mod is not None and hasattr(mod, "pscan"):
-            _swap(mod, "pscan", _p.pscan)
+            _swap(mod, "pscan", _pscan)
     blocks = [sys.modules["mambapy.mamba"].MambaBlock]
     for modname in ("mambapy.vim", "mambapy.onnx.mamba_onnx"):
         mod = sys.modules.get(modname)
