@@ -68,6 +68,34 @@ int mb200_pscan_fwd(const void* A, const void* X, void* H,
                     int64_t h_sb, int64_t h_sl,
                     const float* h0, float* hT, float* ws, int nseg, int dtype, void* stream);
 
+/* ---- PScan forward for callers that must not allocate.  This entry point has no counterpart
+ * in the reference; it exists for hosts of this library that cannot hand it a workspace: an
+ * inference server whose device memory is one arena carved up at start-up, a control loop that
+ * cannot afford the device-wide synchronisation cudaMalloc/cudaFree imply, or a foreign runtime
+ * that reaches this library through the C ABI and has no allocator of its own to call.
+ *
+ * Same arithmetic and arguments as mb200_pscan_fwd, minus `ws`: when the launch is segmented
+ * (nseg > 1) the per-segment aggregates go to a fixed 8 MiB array inside the library image
+ * (mb200_pscan_noalloc_max_ws_floats() floats; every GPU that loads the library keeps it until
+ * the process ends).  nseg == 0 lets the library choose as mb200_pscan_segments would.
+ *   - Limit: 2 * B * nseg * DN floats must fit the array, otherwise MB200_ETOOBIG is returned and
+ *     nothing is launched.  nseg == 1 needs no scratch and has no such limit.
+ *   - The function, and everything it calls, performs no cudaMalloc / cudaFree and calls no
+ *     allocating library routine; inputs and outputs are the caller's.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress
+ *     with that device current; MB200_ESETUP if it fails).  Make that first call before starting
+ *     any stream capture on the device.
+ *   - All calls on a device share the one array, and it keeps whatever the previous call left.
+ *     Each call overwrites the part it uses before reading it, so nothing needs clearing, but two
+ *     calls that overlap on the GPU (different streams, or different host threads) race: keep
+ *     calls of this entry point ordered on one stream per device. */
+int64_t mb200_pscan_noalloc_max_ws_floats(void);
+int mb200_pscan_fwd_noalloc(const void* A, const void* X, void* H,
+                            int64_t B, int64_t L, int64_t DN,
+                            int64_t a_sb, int64_t a_sl, int64_t x_sb, int64_t x_sl,
+                            int64_t h_sb, int64_t h_sl,
+                            const float* h0, float* hT, int nseg, int dtype, void* stream);
+
 /* ---- PScan.apply backward.  Replaces mambapy/pscan.py:188-224 (PScan.backward):
  * gradX[t] = gradH[t] + A[t+1]*gradX[t+1];  gradA[t] = H[t-1]*gradX[t], gradA[0] = 0
  * (or h0*gradX[0] when an incoming state h0 is given).

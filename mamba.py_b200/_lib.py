@@ -22,6 +22,8 @@ _SIGNATURES = {
     "mb200_sscan_chunk": (_int, []),
     "mb200_pscan_segments": (_int, [_i64] * 3),
     "mb200_pscan_fwd": (_int, [_ptr] * 3 + [_i64] * 9 + [_ptr] * 3 + [_int, _int, _ptr]),
+    "mb200_pscan_noalloc_max_ws_floats": (_i64, []),
+    "mb200_pscan_fwd_noalloc": (_int, [_ptr] * 3 + [_i64] * 9 + [_ptr] * 2 + [_int, _int, _ptr]),
     "mb200_pscan_bwd": (_int, [_ptr] * 5 + [_i64] * 13 + [_ptr] * 2 + [_int, _int, _ptr]),
     "mb200_sscan_fwd": (_int, [_ptr] * 12 + [_i64] * 3 + [_int] + [_i64] * 12 + [_int, _int, _ptr]),
     "mb200_sscan_bwd": (_int, [_ptr] * 20 + [_i64] * 3 + [_int] + [_i64] * 18 + [_int, _int, _ptr]),

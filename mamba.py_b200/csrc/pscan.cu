@@ -398,3 +398,63 @@ extern "C" int mb200_pscan_bwd(const void* A, const void* H, const void* gradH, 
                                    g_sb, g_sl, ga_sb, ga_sl, gx_sb, gx_sl, h0, ws, nseg, st);
   return MB200_EDTYPE;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the forward.  The segmented forward needs scratch (the per-segment
+// aggregates).  Callers that cannot obtain device memory at call time get that scratch from a
+// fixed array that lives in the library image instead: every GPU that loads the library holds
+// kStaticWsFloats * 4 bytes (8 MiB) for it until the process exits.
+//
+// In host code `g_static_ws` is only a stand-in symbol, not a device address; the address a
+// kernel can use is looked up once per device with cudaGetSymbolAddress while that device is
+// current, and cached.
+namespace mb200 {
+namespace {
+constexpr int64_t kStaticWsFloats = int64_t(1) << 21;
+static __device__ __align__(256) float g_static_ws[kStaticWsFloats];
+
+constexpr int kMaxDevices = 64;
+float* g_static_ws_addr[kMaxDevices] = {};
+
+// Returns the device address of g_static_ws on the current device, or nullptr on failure.
+float* static_ws_for_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  float* p = __atomic_load_n(&g_static_ws_addr[dev], __ATOMIC_ACQUIRE);
+  if (p) return p;
+  void* addr = nullptr;
+  if (cudaGetSymbolAddress(&addr, g_static_ws) != cudaSuccess || !addr) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  // two threads racing here look up the same address; either store is fine
+  __atomic_store_n(&g_static_ws_addr[dev], static_cast<float*>(addr), __ATOMIC_RELEASE);
+  return static_cast<float*>(addr);
+}
+}  // namespace
+}  // namespace mb200
+
+extern "C" int64_t mb200_pscan_noalloc_max_ws_floats(void) { return kStaticWsFloats; }
+
+extern "C" int mb200_pscan_fwd_noalloc(const void* A, const void* X, void* H, int64_t B, int64_t L,
+                                       int64_t DN, int64_t a_sb, int64_t a_sl, int64_t x_sb,
+                                       int64_t x_sl, int64_t h_sb, int64_t h_sl, const float* h0,
+                                       float* hT, int nseg, int dtype, void* stream) {
+  if (B < 0 || L < 0 || DN < 0 || nseg < 0) return MB200_EINVAL;
+  if (B == 0 || L == 0 || DN == 0) return MB200_OK;
+  if (!A || !X || !H) return MB200_EINVAL;
+  if (dtype != MB200_F32 && dtype != MB200_BF16) return MB200_EDTYPE;
+  if (nseg == 0) nseg = pick_segments(B, L, DN);
+  if (B > 65535 || nseg > 65535) return MB200_ETOOBIG;
+  float* ws = nullptr;
+  if (nseg > 1) {
+    // 2 * B * nseg * DN floats of aggregates must fit the fixed array
+    if (B * int64_t(nseg) > kStaticWsFloats / 2 / DN) return MB200_ETOOBIG;
+    ws = static_ws_for_current_device();
+    if (!ws) return MB200_ESETUP;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == MB200_F32)
+    return fwd_impl<float>(A, X, H, B, L, DN, a_sb, a_sl, x_sb, x_sl, h_sb, h_sl, h0, hT, ws, nseg, st);
+  return fwd_impl<__nv_bfloat16>(A, X, H, B, L, DN, a_sb, a_sl, x_sb, x_sl, h_sb, h_sl, h0, hT, ws, nseg, st);
+}
