@@ -484,8 +484,8 @@ def main():
         if world == 1 and not args.no_cpu_baseline and wl in CPU_SAMPLES:
             line["cpu_baseline"] = cpu_baseline(wl)
         print(json.dumps(line))
-    if world > 1:
-        import torch.distributed as dist
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
 

@@ -32,7 +32,7 @@ enum {
   MB200_OK = 0,
   MB200_EINVAL = -1,      /* bad shape / null pointer / negative size            */
   MB200_EDTYPE = -2,      /* unknown dtype code                                   */
-  MB200_ENSTATE = -3,     /* d_state N not one of the compiled sizes (4,8,16,32,64) */
+  MB200_ENSTATE = -3,     /* d_state N not one of the compiled sizes (8,16,32,64) */
   MB200_EALIGN = -4,      /* a float32 state/carry pointer is not 16-byte aligned */
   MB200_ELAUNCH = -5,     /* the CUDA runtime refused the launch                  */
   MB200_ETOOBIG = -6,     /* size beyond a documented limit of the entry point    */
@@ -153,19 +153,27 @@ int mb200_sscan_bwd(const void* x, const void* delta, const void* z,
                     int64_t dz_sb, int64_t dz_sl,
                     int dtype, int flags, void* stream);
 
-/* ---- Fused decode step.  Replaces the arithmetic of mambapy/mamba.py:384-414
- * (MambaBlock.ssm_step after the projections) and, with conv_w != NULL, also the
- * conv-window part of MambaBlock.step (:366-369, :379) and its gate (:373-375).
- *   xin   : (B, ED) activations.  With conv_w == NULL it is the post-conv, post-SiLU x.
- *           With conv_w != NULL it is the raw x branch of in_proj; the kernel forms the
- *           window [conv_in, xin], applies the depthwise filter conv_w (ED, K) + conv_b (ED)
- *           and SiLU, and writes the shifted window to conv_out (B, ED, K-1).
+/* ---- Reverse carry pass of the sequence-sharded backward (no reference counterpart; the
+ * reference is single-device).  For one shard of the sequence it returns, in g_out (B, ED, N)
+ * float32, the gradient carry a[0]*g[0] that leaves the shard's first timestep when NO carry
+ * enters its last one:  gc <- exp(delta[t]*A) * (dy[t]*silu(z[t])*C[t] + gc),  t = L-1 .. 0.
+ * Reads delta, z (optional), dy, Cm once; needs no hidden states. */
+int mb200_sscan_bwd_carry(const void* delta, const void* z, const void* dy, const void* Cm,
+                          const float* A, const float* delta_bias, float* g_out,
+                          int64_t B, int64_t L, int64_t ED, int N,
+                          int64_t d_sb, int64_t d_sl, int64_t z_sb, int64_t z_sl,
+                          int64_t dy_sb, int64_t dy_sl, int64_t c_sb, int64_t c_sl,
+                          int dtype, int flags, void* stream);
+
+/* ---- Fused decode step.  Replaces the arithmetic of mambapy/mamba.py:398-412
+ * (MambaBlock.ssm_step after the projections) and the gate of MambaBlock.step (:373-375):
+ *   h'[b,e,n] = exp(delta*A[e,n]) * h[b,e,n] + delta*Bm[b,n]*x[b,e]
+ *   y[b,e]    = ( sum_n h'[b,e,n]*Cm[b,n] + D[e]*x[b,e] ) * silu(z[b,e])
+ *   x     : (B, ED) activations, the post-conv, post-SiLU x (see mb200_conv_step).
  *   delta : (B, ED) activations; MB200_DELTA_SOFTPLUS applies softplus(delta + delta_bias).
- *   Bm, Cm: (B, N) activations.  z: (B, ED) or NULL.  h_in: (B, ED, N) float32 or NULL (= 0).
- *   h_out : (B, ED, N) float32 (may alias h_in).  y: (B, ED).
- * Note: when conv_w != NULL, delta/Bm/Cm depend on the post-conv x through x_proj, so the
- * host runs `mb200_conv_step` first; the combined form exists for callers that pass
- * projections computed from the value this function also returns in xc_out. */
+ *   Bm, Cm: (B, N) activations.  z: (B, ED) or NULL (no gate).  D: (ED) or NULL.
+ *   h_in  : (B, ED, N) float32 or NULL (= 0, the reference's h = None first step).
+ *   h_out : (B, ED, N) float32 (may alias h_in).  y: (B, ED).  Row strides *_sb in elements. */
 int mb200_ssm_step(const void* x, const void* delta, const void* z,
                    const float* A, const void* Bm, const void* Cm, const float* D,
                    const float* delta_bias, const float* h_in, float* h_out, void* y,

@@ -27,6 +27,7 @@ _SIGNATURES = {
     "mb200_pscan_bwd": (_int, [_ptr] * 5 + [_i64] * 13 + [_ptr] * 2 + [_int, _int, _ptr]),
     "mb200_sscan_fwd": (_int, [_ptr] * 12 + [_i64] * 3 + [_int] + [_i64] * 12 + [_int, _int, _ptr]),
     "mb200_sscan_bwd": (_int, [_ptr] * 20 + [_i64] * 3 + [_int] + [_i64] * 18 + [_int, _int, _ptr]),
+    "mb200_sscan_bwd_carry": (_int, [_ptr] * 7 + [_i64] * 3 + [_int] + [_i64] * 8 + [_int, _int, _ptr]),
     "mb200_ssm_step": (_int, [_ptr] * 11 + [_i64] * 2 + [_int] + [_i64] * 6 + [_int, _int, _ptr]),
     "mb200_conv_step": (_int, [_ptr] * 6 + [_i64] * 2 + [_int, _i64, _int, _ptr]),
     "mb200_carry_fold": (_int, [_ptr] * 3 + [_i64] * 2 + [_int, _int, _ptr]),

@@ -1,0 +1,222 @@
+"""GPU legs of bench.py for the decode and the sequence-sharded workloads.
+
+Kept inside the package so that bench.py stays a thin driver; the timing helpers are passed in by
+bench.py (one definition of "timed region" for every workload).
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.nn.functional as F
+
+from . import workloads
+from .mamba import ssm_step_fn, conv_step_fn, sscan_fwd_raw, sscan_bwd_raw
+
+
+# ----------------------------------------------------------------------------------- decode
+def _rms(x, w, eps=1e-5):
+    return (x * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + eps).to(x.dtype)) * w
+
+
+def decode_layer_step(W, x, h, win):
+    """One ResidualBlock.step (mambapy/mamba.py:114-125, :351-382) on explicit weights, with the
+    caches updated in place.  x: (B, D); h: (B, ED, N) f32; win: (B, ED, d_conv-1)."""
+    R = W["dt_w"].shape[1]
+    N = W["A"].shape[1]
+    xz = F.linear(_rms(x, W["norm_w"]), W["in_proj"])
+    xs, z = xz.chunk(2, dim=1)
+    xc, _ = conv_step_fn(xs, win, W["conv_w"], W["conv_b"], inplace=True)
+    dbc = F.linear(xc, W["x_proj"])
+    dlt, Bm, Cm = torch.split(dbc, [R, N, N], dim=-1)
+    dlt = F.linear(dlt, W["dt_w"])
+    y, _ = ssm_step_fn(xc, h, dlt, W["A"], Bm, Cm, W["D"], z=z, delta_bias=W["dt_b"], inplace=True)
+    return F.linear(y, W["out_proj"]) + x
+
+
+def bench_decode(args, rank, world, dev, ClockSampler, time_region, time_kernel):
+    """Batched decode, Mamba-2.8b shape: 64 layers, B = 256 single-token inputs per step.
+
+    A "step" is one token for the whole batch through all 64 layers (the reference's Mamba.step),
+    replayed from one CUDA graph; tokens/s = 256 * steps / time."""
+    n_layers = int(os.environ.get("MB200_DECODE_LAYERS", "64"))
+    Bsz, Dm, ED, N, K = 256, 2560, 5120, 16, 4
+    Ws = [workloads.decode_layer_weights(1003 + i, dev) for i in range(n_layers)]
+    gen = torch.Generator(device=dev).manual_seed(1003 + 1000 * rank)
+    hs = [torch.randn(Bsz, ED, N, generator=gen, device=dev) for _ in range(n_layers)]
+    wins = [torch.randn(Bsz, ED, K - 1, generator=gen, device=dev).bfloat16() for _ in range(n_layers)]
+    x_in = torch.randn(Bsz, Dm, generator=gen, device=dev).bfloat16()
+    out = torch.empty_like(x_in)
+
+    def model_step():
+        x = x_in
+        for W, h, win in zip(Ws, hs, wins):
+            x = decode_layer_step(W, x, h, win)
+        out.copy_(x)
+
+    with torch.no_grad():
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(3):
+                model_step()
+        torch.cuda.current_stream().wait_stream(s)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            model_step()
+
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        sampler = ClockSampler(dev.index or 0)
+        sampler.start()
+        ms, t_lo, t_hi = time_region(graph.replay, args.steps, world)
+        res = {"value": Bsz * world * args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
+               "gpu_launches": 2 * n_layers * args.steps}
+
+        # the state-update kernel alone, cycling over the layers' states so every launch misses L2
+        W0 = Ws[0]
+        xc = torch.randn(Bsz, ED, generator=gen, device=dev).bfloat16()
+        dlt = torch.randn(Bsz, ED, generator=gen, device=dev).bfloat16()
+        zz = torch.randn(Bsz, ED, generator=gen, device=dev).bfloat16()
+        Bm = torch.randn(Bsz, N, generator=gen, device=dev).bfloat16()
+        Cm = torch.randn(Bsz, N, generator=gen, device=dev).bfloat16()
+        it = {"i": 0}
+
+        def one():
+            i = it["i"] = (it["i"] + 1) % n_layers
+            ssm_step_fn(xc, hs[i], dlt, W0["A"], Bm, Cm, W0["D"], z=zz, delta_bias=W0["dt_b"], inplace=True)
+
+        xs_raw = torch.randn(Bsz, ED, generator=gen, device=dev).bfloat16()
+
+        def conv_one():
+            i = it["i"] = (it["i"] + 1) % n_layers
+            conv_step_fn(xs_raw, wins[i], W0["conv_w"], W0["conv_b"], inplace=True)
+
+        for _ in range(4):
+            one()
+            conv_one()
+        k_ms, k_min = time_kernel(one, 32)
+        c_ms, c_min = time_kernel(conv_one, 32)
+        state_bytes = 2 * Bsz * ED * N * 4 + 4 * Bsz * ED * 2 + 2 * Bsz * N * 2
+        conv_bytes = 2 * Bsz * ED * (K - 1) * 2 + 2 * Bsz * ED * 2
+        res["kernels"] = {
+            "ssm_step_kernel": {"ms": k_ms, "ms_min": k_min, "algorithmic_bytes": state_bytes,
+                                "GBps": state_bytes / k_ms / 1e6},
+            "conv_step_kernel": {"ms": c_ms, "ms_min": c_min, "algorithmic_bytes": conv_bytes,
+                                 "GBps": conv_bytes / c_ms / 1e6},
+        }
+        res["dominant"] = ("ssm_step_kernel", state_bytes, k_ms)
+
+        # end to end: the token batch comes from pinned host memory, the hidden output goes back
+        hx = x_in.cpu().pin_memory()
+        hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+
+        def e2e_step():
+            x_in.copy_(hx, non_blocking=True)
+            graph.replay()
+            hout.copy_(out, non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        k_e2e = max(3, min(args.steps, 20))
+        ems, _, _ = time_region(e2e_step, k_e2e, world)
+        sampler.stop()
+        nbytes = x_in.numel() * x_in.element_size()
+        res["e2e"] = {"value": Bsz * world * k_e2e / (ems * 1e-3), "unit": "tokens/s",
+                      "h2d_bytes_per_step": nbytes, "d2h_bytes_per_step": nbytes, "steps": k_e2e,
+                      "ms_per_step": ems / k_e2e}
+        res["clocks"] = sampler.summary(t_lo, t_hi)
+        res["n_layers"] = n_layers
+    return res
+
+
+# ---------------------------------------------------------------------------- sequence sharding
+def bench_lshard(args, rank, world, dev, ClockSampler, time_region, time_kernel):
+    """Long sequence split over the ranks along L; fwd+bwd with the carry exchange (strong scaling)."""
+    import torch.distributed as dist
+    from .lshard import selective_scan_lsharded
+    L = int(os.environ.get("MB200_LSHARD_L", "131072"))
+    Bsz, ED, N = 1, 5120, 16
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=dev)
+    Ls = L // world
+    w = workloads.long_scan_inputs(1004, dev, Bsz, L, ED, N, t0=rank * Ls, t1=(rank + 1) * Ls)
+    leaves = {k: w[k].requires_grad_() for k in ("x", "delta", "z", "B", "C", "A", "D")}
+
+    def step():
+        for t in leaves.values():
+            t.grad = None
+        y = selective_scan_lsharded(leaves["x"], leaves["delta"], leaves["A"], leaves["B"], leaves["C"],
+                                    leaves["D"], z=leaves["z"])
+        y.backward(w["dy"])
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    ms, t_lo, t_hi = time_region(step, args.steps, world)
+    res = {"value": Bsz * L * args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
+           "gpu_launches": 8 * args.steps}
+
+    d = {k: w[k].detach() for k in ("x", "delta", "z", "B", "C", "A", "D", "dy")}
+    keep = {}
+
+    def fwd():
+        keep["o"] = sscan_fwd_raw(d["x"], d["delta"], d["A"], d["B"], d["C"], d["D"], d["z"], want_carries=True)
+
+    fwd()
+
+    def bwd():
+        keep["g"] = sscan_bwd_raw(d["x"], d["delta"], d["A"], d["B"], d["C"], d["D"], d["z"], None, d["dy"],
+                                  keep["o"][2])
+
+    for f in (fwd, bwd, fwd, bwd):
+        f()
+    fwd_ms, fwd_min = time_kernel(fwd, 5)
+    bwd_ms, bwd_min = time_kernel(bwd, 5)
+    sampler.stop()
+    fwd_bytes = (4 * ED + 2 * N) * 2 * Bsz * Ls
+    bwd_bytes = (7 * ED + 4 * N) * 2 * Bsz * Ls
+    res["kernels"] = {
+        "sscan_fwd_kernel": {"ms": fwd_ms, "ms_min": fwd_min, "algorithmic_bytes": fwd_bytes,
+                             "GBps": fwd_bytes / fwd_ms / 1e6},
+        "sscan_bwd_kernel": {"ms": bwd_ms, "ms_min": bwd_min, "algorithmic_bytes": bwd_bytes,
+                             "GBps": bwd_bytes / bwd_ms / 1e6},
+    }
+    res["dominant"] = ("sscan_bwd_kernel", bwd_bytes, bwd_ms)
+    res["clocks"] = sampler.summary(t_lo, t_hi)
+
+    if not args.skip_e2e:
+        # end to end on a bounded slice of the shard (the whole shard would pin > 10 GB of host memory)
+        n = min(Ls, 16384)
+        host_in = {k: d[k][:, :n].cpu().pin_memory() for k in ("x", "delta", "z", "B", "C", "dy")}
+        dev_in = {k: torch.empty_like(d[k][:, :n]) for k in host_in}
+        host_out = []
+
+        def e2e_step():
+            for k in host_in:
+                dev_in[k].copy_(host_in[k], non_blocking=True)
+            lv = {k: dev_in[k].requires_grad_() for k in ("x", "delta", "z", "B", "C")}
+            for t in lv.values():
+                t.grad = None
+            y = selective_scan_lsharded(lv["x"], lv["delta"], d["A"], lv["B"], lv["C"], d["D"], z=lv["z"])
+            y.backward(dev_in["dy"])
+            outs = [y.detach()] + [lv[k].grad for k in ("x", "delta", "z", "B", "C")]
+            if not host_out:
+                host_out.extend(torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs)
+            for h, o in zip(host_out, outs):
+                h.copy_(o, non_blocking=True)
+            for k in lv:
+                dev_in[k].requires_grad_(False)
+
+        for _ in range(2):
+            e2e_step()
+        ems, _, _ = time_region(e2e_step, 3, world)
+        res["e2e"] = {"value": n * world * 3 / (ems * 1e-3), "unit": "tokens/s",
+                      "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host_in.values()),
+                      "d2h_bytes_per_step": sum(t.numel() * t.element_size() for t in host_out),
+                      "steps": 3, "ms_per_step": ems / 3,
+                      "note": f"first {n} timesteps of each rank's shard per step"}
+    return res

@@ -170,11 +170,12 @@ def selective_scan_seq(self, x, delta, A, B, C, D):
     return selective_scan_fn(x, delta, A, B, C, D)
 
 
-def ssm_step_fn(x, h, delta, A, B, C, D=None, z=None, delta_bias=None):
+def ssm_step_fn(x, h, delta, A, B, C, D=None, z=None, delta_bias=None, inplace=False):
     """One decode step on projected inputs.  x, delta, z: (B, ED); B, C: (B, N); h: (B, ED, N) or None.
 
     Returns (y, h_new); h_new is a fresh float32 tensor (the reference also returns a new one,
-    mambapy/mamba.py:408)."""
+    mambapy/mamba.py:408).  `inplace=True` (opt-in, for decode loops that own their cache)
+    overwrites a float32 contiguous `h` instead and returns it."""
     _require_cuda(x, delta, A, B, C, D, z, delta_bias, h)
     lib = _lib.load()
     dt = _act_dtype(x)
@@ -183,7 +184,12 @@ def ssm_step_fn(x, h, delta, A, B, C, D=None, z=None, delta_bias=None):
     h32 = None if h is None else h.float().contiguous()
     Bsz, ED = xs.shape
     N = A32.shape[1]
-    h_new = torch.empty((Bsz, ED, N), dtype=torch.float32, device=xs.device)
+    if inplace:
+        if h is None or h32.data_ptr() != h.data_ptr():
+            raise ValueError("inplace=True needs a float32 contiguous state tensor")
+        h_new = h
+    else:
+        h_new = torch.empty((Bsz, ED, N), dtype=torch.float32, device=xs.device)
     y = torch.empty((Bsz, ED), dtype=dt, device=xs.device)
     flags = _lib.DELTA_SOFTPLUS if b32 is not None else 0
     with torch.cuda.device(xs.device):
@@ -196,12 +202,13 @@ def ssm_step_fn(x, h, delta, A, B, C, D=None, z=None, delta_bias=None):
     return y, h_new
 
 
-def conv_step_fn(x, inputs, weight, bias):
+def conv_step_fn(x, inputs, weight, bias, inplace=False):
     """Conv-window part of a decode step (mambapy/mamba.py:366-369, :379).
 
     x: (B, ED) new pre-conv input; inputs: (B, ED, d_conv-1) cached window;
     weight: (ED, 1, d_conv) depthwise filter; bias: (ED) or None.
-    Returns (silu(conv(x)), new window)."""
+    Returns (silu(conv(x)), new window).  The window is a fresh tensor unless `inplace=True`
+    (opt-in), which shifts a contiguous window of the activation dtype in place."""
     _require_cuda(x, inputs, weight, bias)
     lib = _lib.load()
     dt = _act_dtype(x)
@@ -212,7 +219,12 @@ def conv_step_fn(x, inputs, weight, bias):
     w32 = weight.detach().reshape(ED, K).float().contiguous()
     b32 = _f32(bias)
     xc = torch.empty((Bsz, ED), dtype=dt, device=xs.device)
-    new_win = torch.empty_like(win)
+    if inplace:
+        if win.data_ptr() != inputs.data_ptr():
+            raise ValueError("inplace=True needs a contiguous window of the activation dtype")
+        new_win = inputs
+    else:
+        new_win = torch.empty_like(win)
     with torch.cuda.device(xs.device):
         rc = lib.mb200_conv_step(xs.data_ptr(), win.data_ptr(), w32.data_ptr(), _lib.ptr(b32),
                                  xc.data_ptr(), new_win.data_ptr(), Bsz, ED, K, xs.stride(0),

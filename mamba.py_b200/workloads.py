@@ -107,8 +107,8 @@ def decode_layer_weights(seed: int, device, d_model=2560, N=16, d_conv=4, dtype=
     return dict(
         norm_w=torch.ones(d_model, device=device, dtype=dtype),
         in_proj=u((2 * ED, d_model), 1 / math.sqrt(d_model)).to(dtype),
-        conv_w=u((ED, 1, d_conv), 1 / math.sqrt(d_conv)).to(dtype),
-        conv_b=u((ED,), 1 / math.sqrt(d_conv)).to(dtype),
+        conv_w=u((ED, 1, d_conv), 1 / math.sqrt(d_conv)),      # the kernel takes the filter in float32
+        conv_b=u((ED,), 1 / math.sqrt(d_conv)),
         x_proj=u((R + 2 * N, ED), 1 / math.sqrt(ED)).to(dtype),
         dt_w=u((ED, R), R ** -0.5).to(dtype),
         dt_b=dt_bias_init(ED, gen, device),
