@@ -48,6 +48,12 @@ enum {
 const char* mb200_strerror(int code);
 int mb200_version(void);
 
+/* Device-side status of the kernels launched so far on the current device: 0, or 1 when a
+ * bounded wait between the producer and consumer warps of the fused scan gave up (the launch's
+ * outputs are then invalid).  Reads and clears the word; SYNCHRONISES the device, so it is for
+ * tests and diagnostics, not for the hot path.  Returns -1 if the word cannot be read. */
+int mb200_device_status(void);
+
 /* Number of timesteps between two saved scan states ("chunk carries").  The carries
  * tensor of the fused scan has shape (B, ceil(L / chunk), ED, N), float32. */
 int mb200_sscan_chunk(void);

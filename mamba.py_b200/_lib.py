@@ -19,6 +19,7 @@ _i64, _int, _ptr = C.c_int64, C.c_int, C.c_void_p
 _SIGNATURES = {
     "mb200_strerror": (C.c_char_p, [_int]),
     "mb200_version": (_int, []),
+    "mb200_device_status": (_int, []),
     "mb200_sscan_chunk": (_int, []),
     "mb200_pscan_segments": (_int, [_i64] * 3),
     "mb200_pscan_fwd": (_int, [_ptr] * 3 + [_i64] * 9 + [_ptr] * 3 + [_int, _int, _ptr]),

@@ -57,6 +57,14 @@ __device__ __forceinline__ float softplusf(float x) {   // torch semantics: thre
   return x > 20.f ? x : log1pf(__expf(x));
 }
 __device__ __forceinline__ float sigmoidf(float x) { return 1.f / (1.f + __expf(-x)); }
+// Cheaper forms for the streaming kernels: approximate reciprocal / logarithm, with a short
+// series where 1 + e^x would lose the small term to rounding.  Relative error below 1e-5.
+__device__ __forceinline__ float sigmoid_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+__device__ __forceinline__ float softplus_fast(float x) {
+  if (x > 20.f) return x;
+  const float e = __expf(x);
+  return e < 1e-2f ? e * (1.f - e * (0.5f - e * (1.f / 3.f))) : __logf(1.f + e);
+}
 
 // ---- packed float2 arithmetic (one issue slot for two lanes of FMA work) ------------
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
@@ -81,6 +89,40 @@ __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
       : "=f"(d.x), "=f"(d.y)
       : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
   return d;
+}
+
+// ---- CTA-local mbarriers with bounded waits --------------------------------------------
+// Producer and consumer warps of one CTA hand tiles to each other through these.  A wait
+// that does not complete within kSpinLimit polls gives up and reports it; nothing spins
+// without a limit.
+constexpr int kSpinLimit = 1 << 22;
+enum { MB200_DEV_OK = 0, MB200_DEV_WAIT_TIMEOUT = 1 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// true when the phase with the given parity has completed; false after kSpinLimit polls
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (int i = 0; i < kSpinLimit; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
 }
 
 // ---- host-side helpers ----------------------------------------------------------------

@@ -2,194 +2,327 @@
 // SiLU(z) gate in one pass.  Reads x, delta, z, B, C once; writes y (and, for training,
 // the scan state every kChunk timesteps).  The (B, L, ED, N) tensors never exist.
 //
-// Mapping.  The kernel is bound by the exponential (one ex2 per (b, t, e, n)) and the FP32
-// pipe, not by HBM, so it does no redundant arithmetic: every recurrence is walked serially
-// along L by exactly one thread.  A thread owns 4 consecutive states n of one channel e
-// (N/4 lanes share a channel), a CTA owns a tile of channels of one batch row and streams
-// over time in tiles of kTT timesteps staged in shared memory with register prefetch of the
-// next tile.  The partial C-contractions of kLPE consecutive timesteps are transposed across
-// the kLPE lanes of a channel, so each lane finishes (D skip, gate, store) one timestep.
-#include "common.cuh"
-#include "tile.cuh"
-#include "sscan.cuh"
+// What bounds it.  Per (b, t, e, n) element the kernel needs one ex2 (16/clk/SM on the MUFU
+// pipe), four FP32 operations, and its B and C operands out of shared memory; HBM traffic is
+// 0.5 byte per element.  Measured on B200 the recurrence loop alone runs at the shared-memory
+// return bandwidth (128 B/clk/SM), ahead of the MUFU pipe and far ahead of HBM, and the
+// per-(t, e) work around it (softplus, delta*x, D skip, gate, conversions) is 70 % as many
+// instructions again.  So: no redundant arithmetic (every recurrence is walked serially along L
+// by exactly one thread), and everything that is not the recurrence runs on other warps.
+//
+// Structure (this file, used whenever the tensors satisfy the tensor-map alignment rules;
+// sscan_fwd_generic.cuh holds the register-staged path for everything else):
+// a CTA of 256 threads owns a tile of channels of one batch row and walks time in tiles of 16.
+//   - One thread issues TMA loads (cp.async.bulk.tensor, 3-D maps {channels, L, B}) of the raw
+//     x, delta, z, B, C boxes two tiles ahead into a 4-stage shared-memory ring; ragged L and
+//     ragged channel tiles are zero-filled by the copy engine.
+//   - 4 producer warps turn a raw tile into float32 operands ({softplus(delta+bias), delta*x},
+//     B, C; swizzled, double-buffered) and, two tiles later, finish it: sum the N/4 partial
+//     C-contractions per channel, add D*x, apply the SiLU(z) gate, store y.
+//   - 4 consumer warps run nothing but the recurrence: a thread owns 4 consecutive states of one
+//     channel; per timestep 3 shared loads, 4 ex2, 8 packed f32x2 operations and one 4-byte
+//     store of its partial C-contraction.
+//   - Hand-off through CTA-local mbarriers.  Every wait is bounded: a wait that gives up records
+//     MB200_DEV_WAIT_TIMEOUT and the thread leaves the kernel, so nothing can spin forever.
+#include "sscan_fwd_generic.cuh"
+#include "tma.cuh"
 
 namespace mb200 {
 namespace {
 
-template <typename T, int N, int KV>
-__global__ void __launch_bounds__(kThreadsPerCta)
-sscan_fwd_kernel(const SscanFwdParams p) {
-  using G = SscanGeom<N>;
-  constexpr int kLPE = G::kLPE, kTE = G::kTE, kTT = G::kTT;
-  constexpr int KVB = (N % KV == 0) ? KV : 1;
-  using ActRegs = TileRegs<T, kTT, kTE, KV>;
-  using BcRegs = TileRegs<T, kTT, N, KVB>;
+constexpr int kStages = 4;                 // raw-tile ring
+constexpr int kTmaProducers = 128;
+constexpr int kTmaThreads = kConsumers + kTmaProducers;
+constexpr int kTile = kChunk;              // timesteps per tile (= carry spacing)
 
-  __shared__ __align__(16) float2 s_dd[2][kTT][kTE];   // {delta, delta*x}
-  __shared__ __align__(16) float2 s_xz[2][kTT][kTE];   // {x, z}
-  __shared__ __align__(16) float s_B[2][kTT][N];
-  __shared__ __align__(16) float s_C[2][kTT][N];
-  __shared__ __align__(16) T s_y[kTT][kTE];
+// four consecutive channels of one timestep, moved with one 8- or 16-byte access
+template <typename T> struct alignas(sizeof(T) * 4) Vec4 {
+  T v[4];
+};
+
+struct FwdMaps {
+  CUtensorMap x, d, z, B, C;
+};
+
+template <typename T, int N> struct TmaFwdSmem {
+  using G = SscanGeom<N>;
+  static constexpr int kTE = G::kTE;
+  static constexpr int kActBytes = kTile * kTE * int(sizeof(T));       // one raw x / delta / z box
+  static constexpr int kBcBytes = kTile * N * int(sizeof(T));          // one raw B / C box
+  static constexpr int kStageBytes = 3 * kActBytes + 2 * kBcBytes;
+  static_assert(kActBytes % 128 == 0 && kBcBytes % 128 == 0, "TMA destinations stay 128-byte aligned");
+  // byte offsets
+  static constexpr int kRaw = 0;
+  static constexpr int kOp = kRaw + kStages * kStageBytes;              // float2 [2][kTile][kTE]
+  static constexpr int kB = kOp + 2 * kTile * kTE * 8;                  // float  [2][kTile][N]
+  static constexpr int kC = kB + 2 * kTile * N * 4;
+  static constexpr int kYp = kC + 2 * kTile * N * 4;                    // float  [2][kTile][128]
+  static constexpr int kD = kYp + 2 * kTile * kConsumers * 4;           // float  [kTE]
+  static constexpr int kBias = kD + kTE * 4;
+  static constexpr int kBars = kBias + kTE * 4;                         // 12 x uint64
+  static constexpr int kBytes = kBars + 12 * 8;
+};
+
+template <typename T, int N>
+__global__ void __launch_bounds__(kTmaThreads, 3)
+sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams p) {
+  using G = SscanGeom<N>;
+  using S = TmaFwdSmem<T, N>;
+  constexpr int kLPE = G::kLPE, kTE = G::kTE;
+
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  float2* s_op = reinterpret_cast<float2*>(smem_raw + S::kOp);
+  float* s_B = reinterpret_cast<float*>(smem_raw + S::kB);
+  float* s_C = reinterpret_cast<float*>(smem_raw + S::kC);
+  float* s_yp = reinterpret_cast<float*>(smem_raw + S::kYp);
+  float* s_D = reinterpret_cast<float*>(smem_raw + S::kD);
+  float* s_bias = reinterpret_cast<float*>(smem_raw + S::kBias);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + S::kBars);
+  uint64_t* raw_full = bars;            // [kStages] copy landed
+  uint64_t* raw_free = bars + 4;        // [kStages] producers are done with the stage
+  uint64_t* op_full = bars + 8;         // [2] operands committed
+  uint64_t* op_empty = bars + 10;       // [2] consumers are done with the buffer
 
   const int tid = threadIdx.x;
-  const int e_l = tid / kLPE, q = tid % kLPE;
   const int64_t e0 = int64_t(blockIdx.x) * kTE;
-  const int64_t e = e0 + e_l;
   const int64_t b = blockIdx.y;
-  const bool e_ok = e < p.ED;
   const int cols_ok = int(min64(kTE, p.ED - e0));
-
-  const T* gx = static_cast<const T*>(p.x) + b * p.x_sb + e0;
-  const T* gd = static_cast<const T*>(p.delta) + b * p.d_sb + e0;
-  const T* gz = p.z ? static_cast<const T*>(p.z) + b * p.z_sb + e0 : nullptr;
-  const T* gB = static_cast<const T*>(p.Bm) + b * p.b_sb;
-  const T* gC = static_cast<const T*>(p.Cm) + b * p.c_sb;
-  T* gy = p.y ? static_cast<T*>(p.y) + b * p.y_sb + e0 : nullptr;
-
-  float A2[4], h[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    A2[j] = e_ok ? p.A[e * N + 4 * q + j] * kLog2e : 0.f;
-    h[j] = (e_ok && p.h0) ? p.h0[(b * p.ED + e) * N + 4 * q + j] : 0.f;
-  }
-  const float Dv = (e_ok && p.D) ? p.D[e] : 0.f;
   const bool softplus = (p.flags & MB200_DELTA_SOFTPLUS) != 0;
+  const bool has_y = p.y != nullptr;
+  const bool has_z = p.z != nullptr;
+  const int64_t ntiles = (p.L + kTile - 1) / kTile;
 
-  ActRegs rx, rd, rz;
-  BcRegs rB, rC;
-
-  auto fetch = [&](int64_t t0) {
-    const int rows_ok = int(min64(kTT, p.L - t0));
-    rx.load(gx + t0 * p.x_sl, p.x_sl, rows_ok, cols_ok, tid);
-    rd.load(gd + t0 * p.d_sl, p.d_sl, rows_ok, cols_ok, tid);
-    if (gz) rz.load(gz + t0 * p.z_sl, p.z_sl, rows_ok, cols_ok, tid);
-    rB.load(gB + t0 * p.b_sl, p.b_sl, rows_ok, N, tid);
-    rC.load(gC + t0 * p.c_sl, p.c_sl, rows_ok, N, tid);
-  };
-  auto commit = [&](int buf, int64_t t0) {
-    const int rows_ok = int(min64(kTT, p.L - t0));
+  if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < ActRegs::Map::kPerThread; ++i) {
-      if (!ActRegs::Map::owns(i, tid)) continue;
-      const int rr = ActRegs::Map::row(i, tid), cc = ActRegs::Map::col(i, tid);
-#pragma unroll
-      for (int k = 0; k < KV; ++k) {
-        const bool ok = rr < rows_ok && cc + k < cols_ok;
-        float dv = Elem<T>::to_f(rd.r[i].v[k]);
-        const float xv = Elem<T>::to_f(rx.r[i].v[k]);
-        if (softplus) dv = ok ? softplusf(dv + p.delta_bias[e0 + cc + k]) : 0.f;
-        s_dd[buf][rr][cc + k] = make_float2(dv, dv * xv);
-        s_xz[buf][rr][cc + k] = make_float2(xv, gz ? Elem<T>::to_f(rz.r[i].v[k]) : 0.f);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < BcRegs::Map::kPerThread; ++i) {
-      if (!BcRegs::Map::owns(i, tid)) continue;
-      const int rr = BcRegs::Map::row(i, tid), cc = BcRegs::Map::col(i, tid);
-#pragma unroll
-      for (int k = 0; k < KVB; ++k) {
-        s_B[buf][rr][cc + k] = Elem<T>::to_f(rB.r[i].v[k]);
-        s_C[buf][rr][cc + k] = Elem<T>::to_f(rC.r[i].v[k]);
-      }
-    }
-  };
-
-  const int64_t ntiles = (p.L + kTT - 1) / kTT;
-  const int64_t nchunks = (p.L + kChunk - 1) / kChunk;
-  fetch(0);
-  commit(0, 0);
+    for (int i = 0; i < kStages; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_free[i], kTmaProducers); }
+    mbar_init(&op_full[0], kTmaProducers); mbar_init(&op_full[1], kTmaProducers);
+    mbar_init(&op_empty[0], kConsumers); mbar_init(&op_empty[1], kConsumers);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = tid; i < kTE; i += kTmaThreads) {
+    const bool ok = i < cols_ok;
+    s_D[i] = (ok && p.D) ? p.D[e0 + i] : 0.f;
+    s_bias[i] = (ok && softplus) ? p.delta_bias[e0 + i] : 0.f;
+  }
   __syncthreads();
 
-  for (int64_t k = 0; k < ntiles; ++k) {
-    const int buf = int(k & 1);
-    const int64_t t0 = k * kTT;
-    if (k + 1 < ntiles) fetch(t0 + kTT);
-
-#pragma unroll 1
-    for (int w = 0; w < kTT / kLPE; ++w) {
-      float yp[kLPE];
+  if (tid < kConsumers) {
+    // ------------------------------------------------------------------ consumers
+    const int e_l = tid / kLPE, q = tid % kLPE;
+    const int64_t e = e0 + e_l;
+    const bool e_ok = e < p.ED;
+    float2 A2lo, A2hi, hlo, hhi;
+    {
+      float a4[4], h4[4];
 #pragma unroll
-      for (int i = 0; i < kLPE; ++i) {
-        const int t = w * kLPE + i;
-        if (p.carries && (t % kChunk) == 0 && t0 + t < p.L && e_ok) {
-          float4* dst = reinterpret_cast<float4*>(
-              p.carries + ((b * nchunks + (t0 + t) / kChunk) * p.ED + e) * N + 4 * q);
-          *dst = make_float4(h[0], h[1], h[2], h[3]);
-        }
-        const float2 dd = s_dd[buf][t][e_l];
-        const float4 Bq = *reinterpret_cast<const float4*>(&s_B[buf][t][4 * q]);
-        const float4 Cq = *reinterpret_cast<const float4*>(&s_C[buf][t][4 * q]);
-        const float bq[4] = {Bq.x, Bq.y, Bq.z, Bq.w};
-        const float cq[4] = {Cq.x, Cq.y, Cq.z, Cq.w};
-        float acc = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float a = ex2f(dd.x * A2[j]);
-          h[j] = fmaf(a, h[j], dd.y * bq[j]);
-          acc = fmaf(h[j], cq[j], acc);
-        }
-        yp[i] = acc;
+      for (int j = 0; j < 4; ++j) {
+        a4[j] = e_ok ? p.A[e * N + 4 * q + j] * kLog2e : 0.f;
+        h4[j] = (e_ok && p.h0) ? p.h0[(b * p.ED + e) * N + 4 * q + j] : 0.f;
       }
-      if (gy) {
-        // transpose-reduce: lane q ends with the full sum of timestep w*kLPE + q
+      A2lo = make_float2(a4[0], a4[1]); A2hi = make_float2(a4[2], a4[3]);
+      hlo = make_float2(h4[0], h4[1]); hhi = make_float2(h4[2], h4[3]);
+    }
+    const int op_off0 = op_index(0, e_l, kTE), op_off1 = op_index(1, e_l, kTE) - kTE;
+    const int yp_off0 = yp_slot<kLPE, kTE>(0, e_l) * kLPE + q;
+    const int yp_off1 = yp_slot<kLPE, kTE>(1, e_l) * kLPE + q;
+    float* carry_dst = (p.carries && e_ok) ? p.carries + ((b * ntiles) * p.ED + e) * N + 4 * q : nullptr;
+
+    for (int64_t kt = 0; kt < ntiles; ++kt) {
+      const int buf = int(kt & 1);
+      if (!mbar_wait(&op_full[buf], int((kt >> 1) & 1))) {
+        atomicExch(&g_fwd_status, MB200_DEV_WAIT_TIMEOUT);
+        return;
+      }
+      if (carry_dst) {                                  // state entering this 16-step chunk
+        *reinterpret_cast<float4*>(carry_dst) = make_float4(hlo.x, hlo.y, hhi.x, hhi.y);
+        carry_dst += p.ED * N;
+      }
+      const float2* op = s_op + buf * kTile * kTE;
+      const float* sB = s_B + buf * kTile * N + 4 * q;
+      const float* sC = s_C + buf * kTile * N + 4 * q;
+      float* yp = s_yp + buf * kTile * kConsumers;
 #pragma unroll
-        for (int s = kLPE / 2; s >= 1; s >>= 1) {
-          const bool up = (q & s) != 0;
+      for (int t = 0; t < kTile; ++t) {
+        const float2 o = op[t * kTE + ((t & 1) ? op_off1 : op_off0)];   // {delta, delta*x}
+        const float4 Bq = *reinterpret_cast<const float4*>(sB + t * N);
+        const float4 Cq = *reinterpret_cast<const float4*>(sC + t * N);
+        const float2 dd = make_float2(o.x, o.x), dxx = make_float2(o.y, o.y);
+        const float2 e_lo = __fmul2_rn(dd, A2lo), e_hi = __fmul2_rn(dd, A2hi);
+        const float2 a_lo = make_float2(ex2f(e_lo.x), ex2f(e_lo.y));
+        const float2 a_hi = make_float2(ex2f(e_hi.x), ex2f(e_hi.y));
+        const float2 u_lo = __fmul2_rn(dxx, make_float2(Bq.x, Bq.y));
+        const float2 u_hi = __fmul2_rn(dxx, make_float2(Bq.z, Bq.w));
+        hlo = __ffma2_rn(a_lo, hlo, u_lo);
+        hhi = __ffma2_rn(a_hi, hhi, u_hi);
+        float2 acc = __fmul2_rn(hlo, make_float2(Cq.x, Cq.y));
+        acc = __ffma2_rn(hhi, make_float2(Cq.z, Cq.w), acc);
+        if (has_y) yp[t * kConsumers + ((t & 1) ? yp_off1 : yp_off0)] = acc.x + acc.y;
+      }
+      mbar_arrive(&op_empty[buf]);
+    }
+    if (p.hT && e_ok)
+      *reinterpret_cast<float4*>(p.hT + (b * p.ED + e) * N + 4 * q) = make_float4(hlo.x, hlo.y, hhi.x, hhi.y);
+  } else {
+    // ------------------------------------------------------------------ producers
+    const int pt = tid - kConsumers;
+    constexpr int kVecs = kTile * kTE / 4;                 // 4-channel vectors per activation tile
+    constexpr int kVecPerRow = kTE / 4;
+    T* gy = has_y ? static_cast<T*>(p.y) + b * p.y_sb + e0 : nullptr;
+    const uint32_t stage_tx = uint32_t((has_z ? 3 : 2) * S::kActBytes + 2 * S::kBcBytes);
+
+    auto stage_ptr = [&](int64_t kt) { return smem_raw + S::kRaw + int(kt % kStages) * S::kStageBytes; };
+    auto fail = [&]() { atomicExch(&g_fwd_status, MB200_DEV_WAIT_TIMEOUT); };
+
+    // one thread: start the copies of tile kt into its ring stage
+    auto issue = [&](int64_t kt) -> bool {
+      const int r = int(kt % kStages);
+      if (kt >= kStages && !mbar_wait(&raw_free[r], int((kt / kStages - 1) & 1))) return false;
+      unsigned char* st = stage_ptr(kt);
+      const int t0 = int(kt * kTile);
+      mbar_expect_tx(&raw_full[r], stage_tx);
+      tma_load_3d(st, &maps.x, int(e0), t0, int(b), &raw_full[r]);
+      tma_load_3d(st + S::kActBytes, &maps.d, int(e0), t0, int(b), &raw_full[r]);
+      if (has_z) tma_load_3d(st + 2 * S::kActBytes, &maps.z, int(e0), t0, int(b), &raw_full[r]);
+      tma_load_3d(st + 3 * S::kActBytes, &maps.B, 0, t0, int(b), &raw_full[r]);
+      tma_load_3d(st + 3 * S::kActBytes + S::kBcBytes, &maps.C, 0, t0, int(b), &raw_full[r]);
+      return true;
+    };
+    // raw tile kt -> float32 operands in buffer kt & 1
+    auto convert = [&](int64_t kt) {
+      const int buf = int(kt & 1);
+      const int rows_ok = int(min64(kTile, p.L - kt * kTile));
+      const unsigned char* st = stage_ptr(kt);
+      const T* rx = reinterpret_cast<const T*>(st);
+      const T* rd = reinterpret_cast<const T*>(st + S::kActBytes);
+      float2* tile = s_op + buf * kTile * kTE;
+      for (int v = pt; v < kVecs; v += kTmaProducers) {
+        const int rr = v / kVecPerRow, cc = (v % kVecPerRow) * 4;
+        const Vec4<T> xv = *reinterpret_cast<const Vec4<T>*>(rx + rr * kTE + cc);
+        const Vec4<T> dv4 = *reinterpret_cast<const Vec4<T>*>(rd + rr * kTE + cc);
+        float2 o[4];
 #pragma unroll
-          for (int i = 0; i < s; ++i) {
-            const float send = up ? yp[i] : yp[i + s];
-            const float keep = up ? yp[i + s] : yp[i];
-            yp[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+        for (int k = 0; k < 4; ++k) {
+          float dv = Elem<T>::to_f(dv4.v[k]);
+          if (softplus) dv = softplus_fast(dv + s_bias[cc + k]);
+          if (rr >= rows_ok) dv = 0.f;                      // past the end of the sequence
+          o[k] = make_float2(dv, dv * Elem<T>::to_f(xv.v[k]));
+        }
+        *reinterpret_cast<float4*>(tile + op_index(rr, cc, kTE)) = make_float4(o[0].x, o[0].y, o[1].x, o[1].y);
+        *reinterpret_cast<float4*>(tile + op_index(rr, cc + 2, kTE)) = make_float4(o[2].x, o[2].y, o[3].x, o[3].y);
+      }
+      const T* rB = reinterpret_cast<const T*>(st + 3 * S::kActBytes);     // B box then C box, contiguous
+      float* dstB = s_B + buf * kTile * N;
+      float* dstC = s_C + buf * kTile * N;
+      constexpr int kBcVecs = kTile * N / 4;
+      for (int v = pt; v < 2 * kBcVecs; v += kTmaProducers) {
+        const Vec4<T> r4 = *reinterpret_cast<const Vec4<T>*>(rB + v * 4);
+        float* dst = (v < kBcVecs) ? dstB + v * 4 : dstC + (v - kBcVecs) * 4;
+        *reinterpret_cast<float4*>(dst) = make_float4(Elem<T>::to_f(r4.v[0]), Elem<T>::to_f(r4.v[1]),
+                                                      Elem<T>::to_f(r4.v[2]), Elem<T>::to_f(r4.v[3]));
+      }
+    };
+    // finish tile kt: partial sums -> y (the consumers of tile kt have been waited for)
+    auto epilogue = [&](int64_t kt) {
+      const int buf = int(kt & 1);
+      const int64_t t0 = kt * kTile;
+      const int rows_ok = int(min64(kTile, p.L - t0));
+      const unsigned char* st = stage_ptr(kt);
+      const T* rx = reinterpret_cast<const T*>(st);
+      const T* rz = reinterpret_cast<const T*>(st + 2 * S::kActBytes);
+      const float* yp = s_yp + buf * kTile * kConsumers;
+      for (int v = pt; v < kVecs; v += kTmaProducers) {
+        const int rr = v / kVecPerRow, cc = (v % kVecPerRow) * 4;
+        if (rr >= rows_ok || cc >= cols_ok) continue;
+        const Vec4<T> xv = *reinterpret_cast<const Vec4<T>*>(rx + rr * kTE + cc);
+        Vec4<T> zv = xv;
+        if (has_z) zv = *reinterpret_cast<const Vec4<T>*>(rz + rr * kTE + cc);
+        Vec4<T> out;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float s = sum_lanes<kLPE>(yp + rr * kConsumers + yp_slot<kLPE, kTE>(rr, cc + k) * kLPE);
+          float yv = fmaf(s_D[cc + k], Elem<T>::to_f(xv.v[k]), s);
+          if (has_z) {
+            const float zf = Elem<T>::to_f(zv.v[k]);
+            yv *= zf * sigmoid_fast(zf);
           }
+          out.v[k] = Elem<T>::from_f(yv);
         }
-        const int t = w * kLPE + q;
-        const float2 xz = s_xz[buf][t][e_l];
-        float yv = fmaf(Dv, xz.x, yp[0]);
-        if (gz) yv *= xz.y * sigmoidf(xz.y);
-        s_y[t][e_l] = Elem<T>::from_f(yv);
-      }
-    }
-    __syncthreads();
-    if (gy) {
-      // coalesced write of the finished tile (same vector split as the loads)
-      ActRegs ry;
-      const int rows_ok = int(min64(kTT, p.L - t0));
+        T* dst = gy + (t0 + rr) * p.y_sl + cc;
+        if (cc + 4 <= cols_ok) {
+          *reinterpret_cast<Vec4<T>*>(dst) = out;
+        } else {
 #pragma unroll
-      for (int i = 0; i < ActRegs::Map::kPerThread; ++i)
-        if (ActRegs::Map::owns(i, tid))
-          ry.r[i] = *reinterpret_cast<const TVec<T, KV>*>(
-              &s_y[ActRegs::Map::row(i, tid)][ActRegs::Map::col(i, tid)]);
-      ry.store(gy + t0 * p.y_sl, p.y_sl, rows_ok, cols_ok, tid);
-    }
-    if (k + 1 < ntiles) commit(buf ^ 1, t0 + kTT);
-    __syncthreads();
-  }
+          for (int k = 0; k < 4; ++k)
+            if (cc + k < cols_ok) dst[k] = out.v[k];
+        }
+      }
+    };
 
-  if (p.hT && e_ok) {
-    float4* dst = reinterpret_cast<float4*>(p.hT + (b * p.ED + e) * N + 4 * q);
-    *dst = make_float4(h[0], h[1], h[2], h[3]);
+    if (pt == 0) {
+      if (!issue(0)) { fail(); return; }
+      if (ntiles > 1 && !issue(1)) { fail(); return; }
+    }
+    for (int64_t kt = 0; kt < ntiles; ++kt) {
+      if (kt >= 2) {
+        if (!mbar_wait(&op_empty[kt & 1], int(((kt - 2) >> 1) & 1))) { fail(); return; }
+        if (has_y) epilogue(kt - 2);
+        mbar_arrive(&raw_free[(kt - 2) % kStages]);
+      }
+      if (!mbar_wait(&raw_full[kt % kStages], int((kt / kStages) & 1))) { fail(); return; }
+      convert(kt);
+      mbar_arrive(&op_full[kt & 1]);
+      if (pt == 0 && kt + 2 < ntiles && !issue(kt + 2)) { fail(); return; }
+    }
+    for (int64_t kt = ntiles >= 2 ? ntiles - 2 : 0; kt < ntiles; ++kt) {
+      if (!mbar_wait(&op_empty[kt & 1], int((kt >> 1) & 1))) { fail(); return; }
+      if (has_y) epilogue(kt);
+    }
   }
 }
 
 template <typename T, int N>
-int launch_n(const SscanFwdParams& p, bool vec, cudaStream_t st) {
+int tma_launch_n(const SscanFwdParams& p, cudaStream_t st) {
   using G = SscanGeom<N>;
+  using S = TmaFwdSmem<T, N>;
+  constexpr bool bf = sizeof(T) == 2;
+  FwdMaps m;
+  bool ok = tma_encode(&m.x, p.x, bf, p.B, p.L, p.ED, p.x_sb, p.x_sl, G::kTE, kTile) &&
+            tma_encode(&m.d, p.delta, bf, p.B, p.L, p.ED, p.d_sb, p.d_sl, G::kTE, kTile) &&
+            tma_encode(&m.B, p.Bm, bf, p.B, p.L, N, p.b_sb, p.b_sl, N, kTile) &&
+            tma_encode(&m.C, p.Cm, bf, p.B, p.L, N, p.c_sb, p.c_sl, N, kTile);
+  if (ok && p.z) ok = tma_encode(&m.z, p.z, bf, p.B, p.L, p.ED, p.z_sb, p.z_sl, G::kTE, kTile);
+  else if (ok) m.z = m.x;
+  if (!ok) return 1;                                   // caller falls back to the generic path
+  auto k = sscan_fwd_tma_kernel<T, N>;
+  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess)
+    return MB200_ELAUNCH;
   dim3 grid(unsigned((p.ED + G::kTE - 1) / G::kTE), unsigned(p.B));
-  constexpr int KV = Elem<T>::kVec;
-  if (vec) sscan_fwd_kernel<T, N, KV><<<grid, kThreadsPerCta, 0, st>>>(p);
-  else sscan_fwd_kernel<T, N, 1><<<grid, kThreadsPerCta, 0, st>>>(p);
+  k<<<grid, kTmaThreads, S::kBytes, st>>>(m, p);
   return check_launch();
 }
 
 template <typename T>
-int launch_t(const SscanFwdParams& p, int N, bool vec, cudaStream_t st) {
+int tma_launch_t(const SscanFwdParams& p, int N, cudaStream_t st) {
   switch (N) {
-    case 8: return launch_n<T, 8>(p, vec, st);
-    case 16: return launch_n<T, 16>(p, vec, st);
-    case 32: return launch_n<T, 32>(p, vec, st);
-    case 64: return launch_n<T, 64>(p, vec, st);
+    case 8: return tma_launch_n<T, 8>(p, st);
+    case 16: return tma_launch_n<T, 16>(p, st);
+    case 32: return tma_launch_n<T, 32>(p, st);
+    case 64: return tma_launch_n<T, 64>(p, st);
     default: return MB200_ENSTATE;
   }
+}
+
+// The tensor-map path needs 16-byte aligned bases and byte strides, and 8-byte aligned y rows.
+bool tma_path_ok(const SscanFwdParams& p, int N, int es) {
+  const int te = kThreadsPerCta / (N / 4);
+  if (p.L >= (int64_t(1) << 31) || p.ED >= (int64_t(1) << 31)) return false;
+  bool ok = tma_compatible(p.x, p.x_sb, p.x_sl, p.ED, es, te) &&
+            tma_compatible(p.delta, p.d_sb, p.d_sl, p.ED, es, te) &&
+            tma_compatible(p.Bm, p.b_sb, p.b_sl, N, es, N) &&
+            tma_compatible(p.Cm, p.c_sb, p.c_sl, N, es, N);
+  if (p.z) ok = ok && tma_compatible(p.z, p.z_sb, p.z_sl, p.ED, es, te);
+  if (p.y) ok = ok && aligned16(p.y) && (p.y_sl * es) % 16 == 0 && (p.y_sb * es) % 16 == 0;
+  return ok && tma_encoder() != nullptr;
 }
 
 }  // namespace
@@ -198,6 +331,15 @@ int launch_t(const SscanFwdParams& p, int N, bool vec, cudaStream_t st) {
 using namespace mb200;
 
 extern "C" int mb200_sscan_chunk(void) { return kChunk; }
+
+// Reads (and clears) the device-side status word of the forward kernels: non-zero when a bounded
+// wait inside a kernel gave up.  Synchronises the device.
+int mb200_fwd_device_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_fwd_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_fwd_status, &zero, sizeof(int));
+  return v;
+}
 
 extern "C" int mb200_sscan_fwd(const void* x, const void* delta, const void* z, const float* A,
                                const void* Bm, const void* Cm, const float* D,
@@ -230,12 +372,17 @@ extern "C" int mb200_sscan_fwd(const void* x, const void* delta, const void* z, 
   p.x_sb = x_sb; p.x_sl = x_sl; p.d_sb = d_sb; p.d_sl = d_sl; p.z_sb = z_sb; p.z_sl = z_sl;
   p.b_sb = b_sb; p.b_sl = b_sl; p.c_sb = c_sb; p.c_sl = c_sl; p.y_sb = y_sb; p.y_sl = y_sl;
   p.flags = flags;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int es = dtype == MB200_F32 ? 4 : 2;
+  if (tma_path_ok(p, N, es)) {
+    const int rc = dtype == MB200_F32 ? tma_launch_t<float>(p, N, st) : tma_launch_t<__nv_bfloat16>(p, N, st);
+    if (rc <= 0) return rc;                        // launched (0) or failed hard (< 0)
+  }
   const int kv = dtype == MB200_F32 ? 4 : 8;
   bool vec = ED % kv == 0 && aligned16(x) && aligned16(delta) && aligned16(z) && aligned16(y) &&
              aligned16(Bm) && aligned16(Cm);
   for (int64_t s : {x_sb, x_sl, d_sb, d_sl, y_sb, y_sl, b_sb, b_sl, c_sb, c_sl}) vec = vec && s % kv == 0;
   if (z) vec = vec && z_sb % kv == 0 && z_sl % kv == 0;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return dtype == MB200_F32 ? launch_t<float>(p, N, vec, st)
-                            : launch_t<__nv_bfloat16>(p, N, vec, st);
+  return dtype == MB200_F32 ? generic_launch_t<float>(p, N, vec, st)
+                            : generic_launch_t<__nv_bfloat16>(p, N, vec, st);
 }

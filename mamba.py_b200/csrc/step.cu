@@ -6,6 +6,7 @@
 // state (so a warp reads 512 contiguous bytes of h), computes its four decays and partial
 // C-contraction, and the lanes of a channel combine with warp shuffles.
 #include "common.cuh"
+#include "sscan.cuh"
 
 namespace mb200 {
 namespace {
@@ -247,3 +248,5 @@ extern "C" const char* mb200_strerror(int code) {
 }
 
 extern "C" int mb200_version(void) { return 100; }
+
+extern "C" int mb200_device_status(void) { return mb200_fwd_device_status(); }

@@ -45,26 +45,27 @@ __device__ __forceinline__ void tvec_store(T* p, const TVec<T, KV>& r) {
   }
 }
 
-// Static description of how a ROWS x COLS tile is split over the CTA.
-template <int ROWS, int COLS, int KV> struct TileMap {
+// Static description of how a ROWS x COLS tile is split over NT cooperating threads
+// (tid is the thread's index among those NT threads).
+template <int ROWS, int COLS, int KV, int NT = kThreadsPerCta> struct TileMap {
   static_assert(COLS % KV == 0, "tile width must hold whole vectors");
   static constexpr int kVecPerRow = COLS / KV;
   static constexpr int kVecs = ROWS * kVecPerRow;
-  static constexpr int kPerThread = (kVecs + kThreadsPerCta - 1) / kThreadsPerCta;
+  static constexpr int kPerThread = (kVecs + NT - 1) / NT;
   __device__ static __forceinline__ bool owns(int i, int tid) {
-    return tid + i * kThreadsPerCta < kVecs;
+    return tid + i * NT < kVecs;
   }
   __device__ static __forceinline__ int row(int i, int tid) {
-    return (tid + i * kThreadsPerCta) / kVecPerRow;
+    return (tid + i * NT) / kVecPerRow;
   }
   __device__ static __forceinline__ int col(int i, int tid) {
-    return ((tid + i * kThreadsPerCta) % kVecPerRow) * KV;
+    return ((tid + i * NT) % kVecPerRow) * KV;
   }
 };
 
 // Registers of one thread's share of a tile.
-template <typename T, int ROWS, int COLS, int KV> struct TileRegs {
-  using Map = TileMap<ROWS, COLS, KV>;
+template <typename T, int ROWS, int COLS, int KV, int NT = kThreadsPerCta> struct TileRegs {
+  using Map = TileMap<ROWS, COLS, KV, NT>;
   TVec<T, KV> r[Map::kPerThread];
 
   // base points at (row 0, col 0) of the tile; rows >= rows_ok or cols >= cols_ok read as 0.
