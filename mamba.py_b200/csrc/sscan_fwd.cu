@@ -30,7 +30,9 @@
 namespace mb200 {
 namespace {
 
-constexpr int kStages = 4;                 // raw-tile ring
+// Raw-tile ring depth.  Copies are issued kStages - 2 tiles ahead: a box takes a few microseconds
+// to land, several times the ~1 us a tile is worked on, so the ring must hold that many in flight.
+template <typename T> struct Ring { static constexpr int kStages = sizeof(T) == 2 ? 8 : 5; };
 constexpr int kTmaProducers = 128;
 constexpr int kTmaThreads = kConsumers + kTmaProducers;
 constexpr int kTile = kChunk;              // timesteps per tile (= carry spacing)
@@ -46,6 +48,7 @@ struct FwdMaps {
 
 template <typename T, int N> struct TmaFwdSmem {
   using G = SscanGeom<N>;
+  static constexpr int kStages = Ring<T>::kStages;
   static constexpr int kTE = G::kTE;
   static constexpr int kActBytes = kTile * kTE * int(sizeof(T));       // one raw x / delta / z box
   static constexpr int kBcBytes = kTile * N * int(sizeof(T));          // one raw B / C box
@@ -59,8 +62,8 @@ template <typename T, int N> struct TmaFwdSmem {
   static constexpr int kYp = kC + 2 * kTile * N * 4;                    // float  [2][kTile][128]
   static constexpr int kD = kYp + 2 * kTile * kConsumers * 4;           // float  [kTE]
   static constexpr int kBias = kD + kTE * 4;
-  static constexpr int kBars = kBias + kTE * 4;                         // 12 x uint64
-  static constexpr int kBytes = kBars + 12 * 8;
+  static constexpr int kBars = kBias + kTE * 4;                         // (2*kStages + 4) x uint64
+  static constexpr int kBytes = kBars + (2 * kStages + 4) * 8;
 };
 
 template <typename T, int N>
@@ -68,7 +71,7 @@ __global__ void __launch_bounds__(kTmaThreads, 3)
 sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams p) {
   using G = SscanGeom<N>;
   using S = TmaFwdSmem<T, N>;
-  constexpr int kLPE = G::kLPE, kTE = G::kTE;
+  constexpr int kLPE = G::kLPE, kTE = G::kTE, kStages = S::kStages, kAhead = S::kStages - 2;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
   float2* s_op = reinterpret_cast<float2*>(smem_raw + S::kOp);
@@ -79,9 +82,9 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
   float* s_bias = reinterpret_cast<float*>(smem_raw + S::kBias);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + S::kBars);
   uint64_t* raw_full = bars;            // [kStages] copy landed
-  uint64_t* raw_free = bars + 4;        // [kStages] producers are done with the stage
-  uint64_t* op_full = bars + 8;         // [2] operands committed
-  uint64_t* op_empty = bars + 10;       // [2] consumers are done with the buffer
+  uint64_t* raw_free = bars + kStages;  // [kStages] producers are done with the stage
+  uint64_t* op_full = bars + 2 * kStages;       // [2] operands committed
+  uint64_t* op_empty = bars + 2 * kStages + 2;  // [2] consumers are done with the buffer
 
   const int tid = threadIdx.x;
   const int64_t e0 = int64_t(blockIdx.x) * kTE;
@@ -259,8 +262,8 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
     };
 
     if (pt == 0) {
-      if (!issue(0)) { fail(); return; }
-      if (ntiles > 1 && !issue(1)) { fail(); return; }
+      for (int64_t kt = 0; kt < kAhead && kt < ntiles; ++kt)
+        if (!issue(kt)) { fail(); return; }
     }
     for (int64_t kt = 0; kt < ntiles; ++kt) {
       if (kt >= 2) {
@@ -271,7 +274,7 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
       if (!mbar_wait(&raw_full[kt % kStages], int((kt / kStages) & 1))) { fail(); return; }
       convert(kt);
       mbar_arrive(&op_full[kt & 1]);
-      if (pt == 0 && kt + 2 < ntiles && !issue(kt + 2)) { fail(); return; }
+      if (pt == 0 && kt + kAhead < ntiles && !issue(kt + kAhead)) { fail(); return; }
     }
     for (int64_t kt = ntiles >= 2 ? ntiles - 2 : 0; kt < ntiles; ++kt) {
       if (!mbar_wait(&op_empty[kt & 1], int((kt >> 1) & 1))) { fail(); return; }
