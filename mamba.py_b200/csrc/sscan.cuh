@@ -30,6 +30,11 @@ __device__ __forceinline__ int op_index(int t, int c, int te) {
   return t * te + swz(t, c >> 1) * 2 + (c & 1);
 }
 
+// four consecutive channels of one timestep, moved with one 8- or 16-byte access
+template <typename T> struct alignas(sizeof(T) * 4) Vec4 {
+  T v[4];
+};
+
 // Sum of the kLPE partial sums the lanes of one channel left in shared memory.
 template <int kLPE>
 __device__ __forceinline__ float sum_lanes(const float* p) {
@@ -103,3 +108,4 @@ struct SscanBwdParams {
 // Device-side status words of the kernels that contain bounded waits (host functions; each reads
 // and clears its kernel's word, synchronising the device).
 int mb200_fwd_device_status();
+int mb200_bwd_device_status();

@@ -1,346 +1,502 @@
-// Fused selective scan, backward.  One pass over x, delta, z, B, C, dy (read once) that
-// writes dx, ddelta, dz and accumulates dB, dC, dA, dD; the hidden states are recomputed
-// chunk by chunk from the states the forward saved every kChunk timesteps.
+// Fused selective scan, backward.  One pass over x, delta, z, B, C, dy (read once) that writes
+// dx, ddelta, dz and accumulates dB, dC, dA, dD; the hidden states are recomputed chunk by chunk
+// from the states the forward saved every 16 timesteps.
 //
-// Mapping: the same as the forward (a thread owns 4 states n of one channel e and walks time
-// serially), but time runs from the last chunk to the first.  For each chunk of 16 timesteps
-//   phase R  recomputes a[t] = exp(delta[t] A) and h[t] forwards from the saved state and keeps
-//            both in registers (2 x 16 x 4 floats), so the exponential is evaluated once;
-//   phase B  walks the chunk backwards:  g[t] = dy'[t] C[t] + a[t+1] g[t+1]  and from g, h, a
-//            forms every gradient term.
-// Two kinds of sums leave a thread:
-//   over n (dx, ddelta, and y for dz): the N/4 lanes of a channel exchange three partial sums
-//            per timestep through shared memory; one lane per timestep finishes it;
-//   over e (dB, dC): a warp's channels are summed through a per-warp shared-memory transpose,
-//            warps are merged with shared-memory atomics, and the CTA adds its 16 x 2N block to
-//            global memory with one atomic per value.
-#include "common.cuh"
-#include "tile.cuh"
-#include "sscan.cuh"
+// Like the forward, the kernel is bound by shared-memory bandwidth and instruction issue, not by
+// HBM, so the recurrences run on warps that do nothing else (tensor-map path, d_state 16; the
+// register-staged kernel in sscan_bwd_generic.cuh covers every other case).
+//
+// A CTA of 256 threads owns 32 channels of one batch row and walks time BACKWARDS in tiles of 16:
+//   - warp 4 issues TMA loads of the raw x, delta, z, dy, B, C boxes a few tiles ahead into a
+//     shared-memory ring and converts each landed tile into float32 operands
+//     ({softplus(delta+bias), delta*x}, dy*silu(z), B, C; double-buffered).
+//   - warps 0-3 (consumers; a thread owns 4 states of one channel) recompute the states of the
+//     tile forwards from the saved carry, 8 timesteps at a time into registers, and walk them
+//     backwards:  g[t] = dy'[t] C[t] + a[t+1] g[t+1],  da = g h[t-1].  Per timestep a thread
+//     leaves three partial sums over its 4 states (for y, dx, ddelta) and its 8 products for
+//     dB, dC in shared memory, in windows of 2 timesteps.
+//   - warps 5 and 7 finish alternate windows: sum the 4 partials of each channel, form dx, ddelta,
+//     dz (and the running sums for dD and d(delta_bias)), store them.
+//   - warp 6 sums the dB, dC products of each window over the CTA's 32 channels and adds the
+//     result to global memory with vector atomics.
+//   - Hand-off through CTA-local mbarriers; every wait is bounded (see mbar_wait).
+#include "sscan_bwd_generic.cuh"
+#include "tma.cuh"
 
 namespace mb200 {
 namespace {
 
-constexpr int kWin = 4;                       // timesteps per reduction window
-constexpr int kWarps = kThreadsPerCta / 32;
+constexpr int kBN = 16;                      // d_state of this path
+constexpr int kBTE = 32;                     // channels per CTA
+constexpr int kBTile = kChunk;               // timesteps per tile
+constexpr int kHalf = kBTile / 2;            // states kept in registers at a time
+constexpr int kBWin = 2;                     // timesteps per reduction window
+constexpr int kWinsPerTile = kBTile / kBWin;
+constexpr int kBwdThreads = 256;
+constexpr int kEpStride = 34;                // float4 per (t, which, q) row of the dB/dC products
 
-template <typename T, int N> struct BwdSmem {
-  using G = SscanGeom<N>;
-  static constexpr int kTE = G::kTE, kLPE = G::kLPE, kEPW = 32 / G::kLPE;
-  // float offsets of each region inside the dynamic shared memory block
-  static constexpr int kIn = 0;                                   // float4 [2][kChunk][kTE] {delta, delta*x, dy', x}
-  static constexpr int kEp = kIn + 2 * kChunk * kTE * 4;          // float4 [2][kChunk][kTE] {z, dy, dsoftplus, -}
-  static constexpr int kB = kEp + 2 * kChunk * kTE * 4;           // float [2][kChunk][N]
-  static constexpr int kC = kB + 2 * kChunk * N;                  // float [2][kChunk][N]
-  static constexpr int kNred = kC + 2 * kChunk * N;               // float4 [kWin][kThreads+1]
-  static constexpr int kEredB = kNred + kWin * (kThreadsPerCta + 1) * 4;   // float [kWarps][kWin][kEPW][N]
-  static constexpr int kEredStride = kWin * kEPW * N + 16;        // per warp, B part; C part follows
-  static constexpr int kAcc = kEredB + kWarps * 2 * kEredStride;  // float [2][kChunk][N]
-  static constexpr int kOut = kAcc + 2 * kChunk * N;              // float [3][kChunk][kTE]
-  static constexpr int kFloats = kOut + 3 * kChunk * kTE;
-  static constexpr int kBytes = kFloats * 4;
+__device__ int g_bwd_status = MB200_DEV_OK;
+
+template <typename T> struct alignas(sizeof(T) * 2) Vec2 {
+  T v[2];
 };
 
-template <typename T, int N, int KV>
-__global__ void __launch_bounds__(kThreadsPerCta)
-sscan_bwd_kernel(const SscanBwdParams p) {
-  using G = SscanGeom<N>;
-  using S = BwdSmem<T, N>;
-  constexpr int kLPE = G::kLPE, kTE = G::kTE, kEPW = S::kEPW;
-  constexpr int KVB = (N % KV == 0) ? KV : 1;
-  using ActRegs = TileRegs<T, kChunk, kTE, KV>;
-  using BcRegs = TileRegs<T, kChunk, N, KVB>;
+struct BwdMaps {
+  CUtensorMap x, d, z, dy, B, C;
+};
 
-  extern __shared__ __align__(16) float smem[];
-  float4* s_in = reinterpret_cast<float4*>(smem + S::kIn);
-  float4* s_ep = reinterpret_cast<float4*>(smem + S::kEp);
-  float* s_B = smem + S::kB;
-  float* s_C = smem + S::kC;
-  float4* s_nred = reinterpret_cast<float4*>(smem + S::kNred);
-  float* s_acc = smem + S::kAcc;
-  float* s_out = smem + S::kOut;
+template <typename T> struct TmaBwdSmem {
+  static constexpr int kStages = sizeof(T) == 2 ? 6 : 3;
+  static constexpr int kActBytes = kBTile * kBTE * int(sizeof(T));
+  static constexpr int kBcBytes = kBTile * kBN * int(sizeof(T));
+  static constexpr int kStageBytes = 4 * kActBytes + 2 * kBcBytes;       // x, delta, z, dy, B, C
+  static constexpr int kRaw = 0;
+  static constexpr int kOp = kRaw + kStages * kStageBytes;                // float2 [2][16][32]
+  static constexpr int kDyp = kOp + 2 * kBTile * kBTE * 8;                // float  [2][16][32]
+  static constexpr int kB = kDyp + 2 * kBTile * kBTE * 4;                 // float  [2][16][16]
+  static constexpr int kC = kB + 2 * kBTile * kBN * 4;
+  static constexpr int kNp = kC + 2 * kBTile * kBN * 4;                   // float4 [2][kBWin][128]
+  static constexpr int kEp = kNp + 2 * kBWin * 128 * 16;                  // float4 [2][kBWin][2][4][kEpStride]
+  static constexpr int kD = kEp + 2 * kBWin * 2 * 4 * kEpStride * 16;     // float [32]
+  static constexpr int kBias = kD + kBTE * 4;
+  static constexpr int kBars = kBias + kBTE * 4;                          // 2*kStages + 8 mbarriers
+  static constexpr int kBytes = kBars + (2 * kStages + 8) * 8;
+};
 
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int e_l = tid / kLPE, q = tid % kLPE, e_w = lane / kLPE;
-  float* s_eB = smem + S::kEredB + warp * 2 * S::kEredStride;
-  float* s_eC = s_eB + S::kEredStride;
-  const int64_t e0 = int64_t(blockIdx.x) * kTE;
-  const int64_t e = e0 + e_l;
-  const int64_t b = blockIdx.y;
-  const bool e_ok = e < p.ED;
-  const int cols_ok = int(min64(kTE, p.ED - e0));
-  const bool has_z = p.z != nullptr;
-  const bool softplus = (p.flags & MB200_DELTA_SOFTPLUS) != 0;
+// float4 slot of consumer thread `tid` in a row of the n-partials tile (XOR keeps the finishing
+// warps' reads mostly conflict free; writes stay a permutation inside each warp)
+__device__ __forceinline__ int np_slot(int tid) { return tid ^ ((tid >> 3) & 7); }
 
-  const T* gx = static_cast<const T*>(p.x) + b * p.x_sb + e0;
-  const T* gd = static_cast<const T*>(p.delta) + b * p.d_sb + e0;
-  const T* gz = has_z ? static_cast<const T*>(p.z) + b * p.z_sb + e0 : nullptr;
-  const T* gdy = static_cast<const T*>(p.dy) + b * p.dy_sb + e0;
-  const T* gB = static_cast<const T*>(p.Bm) + b * p.b_sb;
-  const T* gC = static_cast<const T*>(p.Cm) + b * p.c_sb;
-  T* odx = static_cast<T*>(p.dx) + b * p.dx_sb + e0;
-  T* odd = static_cast<T*>(p.ddelta) + b * p.dd_sb + e0;
-  T* odz = has_z ? static_cast<T*>(p.dz) + b * p.dz_sb + e0 : nullptr;
-
-  float A2[4], gc[4], dAacc[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    A2[j] = e_ok ? p.A[e * N + 4 * q + j] * kLog2e : 0.f;
-    gc[j] = (e_ok && p.g_in) ? p.g_in[(b * p.ED + e) * N + 4 * q + j] : 0.f;
-    dAacc[j] = 0.f;
-  }
-  const float Dv = (e_ok && p.D) ? p.D[e] : 0.f;
-  float dDacc = 0.f, dbias_acc = 0.f;
-
-  ActRegs rx, rd, rz, rdy;
-  BcRegs rB, rC;
-  const int64_t nchunks = (p.L + kChunk - 1) / kChunk;
-
-  auto fetch = [&](int64_t t0) {
-    const int rows_ok = int(min64(kChunk, p.L - t0));
-    rx.load(gx + t0 * p.x_sl, p.x_sl, rows_ok, cols_ok, tid);
-    rd.load(gd + t0 * p.d_sl, p.d_sl, rows_ok, cols_ok, tid);
-    rdy.load(gdy + t0 * p.dy_sl, p.dy_sl, rows_ok, cols_ok, tid);
-    if (has_z) rz.load(gz + t0 * p.z_sl, p.z_sl, rows_ok, cols_ok, tid);
-    rB.load(gB + t0 * p.b_sl, p.b_sl, rows_ok, N, tid);
-    rC.load(gC + t0 * p.c_sl, p.c_sl, rows_ok, N, tid);
-  };
-  auto commit = [&](int buf, int64_t t0) {
-    const int rows_ok = int(min64(kChunk, p.L - t0));
-#pragma unroll
-    for (int i = 0; i < ActRegs::Map::kPerThread; ++i) {
-      if (!ActRegs::Map::owns(i, tid)) continue;
-      const int rr = ActRegs::Map::row(i, tid), cc = ActRegs::Map::col(i, tid);
-#pragma unroll
-      for (int k = 0; k < KV; ++k) {
-        const bool ok = rr < rows_ok && cc + k < cols_ok;
-        float dv = Elem<T>::to_f(rd.r[i].v[k]);
-        const float xv = Elem<T>::to_f(rx.r[i].v[k]);
-        const float dyv = Elem<T>::to_f(rdy.r[i].v[k]);
-        const float zv = has_z ? Elem<T>::to_f(rz.r[i].v[k]) : 0.f;
-        float spg = 1.f;
-        if (softplus) {
-          const float raw = ok ? dv + p.delta_bias[e0 + cc + k] : 0.f;
-          dv = ok ? softplusf(raw) : 0.f;
-          spg = sigmoidf(raw);
-        }
-        const float dyg = has_z ? dyv * zv * sigmoidf(zv) : dyv;
-        s_in[(buf * kChunk + rr) * kTE + cc + k] = make_float4(dv, dv * xv, dyg, xv);
-        s_ep[(buf * kChunk + rr) * kTE + cc + k] = make_float4(zv, dyv, spg, 0.f);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < BcRegs::Map::kPerThread; ++i) {
-      if (!BcRegs::Map::owns(i, tid)) continue;
-      const int rr = BcRegs::Map::row(i, tid), cc = BcRegs::Map::col(i, tid);
-#pragma unroll
-      for (int k = 0; k < KVB; ++k) {
-        s_B[(buf * kChunk + rr) * N + cc + k] = Elem<T>::to_f(rB.r[i].v[k]);
-        s_C[(buf * kChunk + rr) * N + cc + k] = Elem<T>::to_f(rC.r[i].v[k]);
-      }
-    }
-  };
-  auto load_carry = [&](int64_t c, float (&hp)[4]) {
-    if (e_ok) {
-      const float4 v = *reinterpret_cast<const float4*>(
-          p.carries + ((b * nchunks + c) * p.ED + e) * N + 4 * q);
-      hp[0] = v.x; hp[1] = v.y; hp[2] = v.z; hp[3] = v.w;
-    } else {
-      hp[0] = hp[1] = hp[2] = hp[3] = 0.f;
-    }
-  };
-
-  for (int i = tid; i < 2 * kChunk * N; i += kThreadsPerCta) s_acc[i] = 0.f;
-  float hp_next[4];
-  fetch((nchunks - 1) * kChunk);
-  load_carry(nchunks - 1, hp_next);
-  commit(0, (nchunks - 1) * kChunk);
-  __syncthreads();
-
-  int buf = 0;
-  for (int64_t c = nchunks - 1; c >= 0; --c, buf ^= 1) {
-    const int64_t t0 = c * kChunk;
-    float hp[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) hp[j] = hp_next[j];
-    if (c > 0) {
-      fetch(t0 - kChunk);
-      load_carry(c - 1, hp_next);
-    }
-
-    // ---- phase R: decay factors and states of the chunk, kept in registers
-    float a[kChunk][4], hh[kChunk][4];
-#pragma unroll
-    for (int t = 0; t < kChunk; ++t) {
-      const float4 in = s_in[(buf * kChunk + t) * kTE + e_l];
-      const float4 Bq = *reinterpret_cast<const float4*>(&s_B[(buf * kChunk + t) * N + 4 * q]);
-      const float bq[4] = {Bq.x, Bq.y, Bq.z, Bq.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        a[t][j] = ex2f(in.x * A2[j]);
-        hh[t][j] = fmaf(a[t][j], t ? hh[t - 1][j] : hp[j], in.y * bq[j]);
-      }
-    }
-
-    // ---- phase B: reverse walk, one reduction window of kWin timesteps at a time
-#pragma unroll
-    for (int w = kChunk / kWin - 1; w >= 0; --w) {
-#pragma unroll
-      for (int i = kWin - 1; i >= 0; --i) {
-        const int t = w * kWin + i;
-        const float4 in = s_in[(buf * kChunk + t) * kTE + e_l];
-        const float4 Bq = *reinterpret_cast<const float4*>(&s_B[(buf * kChunk + t) * N + 4 * q]);
-        const float4 Cq = *reinterpret_cast<const float4*>(&s_C[(buf * kChunk + t) * N + 4 * q]);
-        const float bq[4] = {Bq.x, Bq.y, Bq.z, Bq.w};
-        const float cq[4] = {Cq.x, Cq.y, Cq.z, Cq.w};
-        float ypart = 0.f, gBpart = 0.f, wApart = 0.f;
-        float dBp[4], dCp[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float g = fmaf(in.z, cq[j], gc[j]);
-          ypart = fmaf(hh[t][j], cq[j], ypart);
-          dCp[j] = in.z * hh[t][j];
-          dBp[j] = g * in.y;
-          gBpart = fmaf(g, bq[j], gBpart);
-          const float hprev = t ? hh[t - 1][j] : hp[j];
-          const float wv = g * hprev * a[t][j];
-          dAacc[j] = fmaf(wv, in.x, dAacc[j]);
-          wApart = fmaf(wv, A2[j], wApart);
-          gc[j] = a[t][j] * g;
-        }
-        s_nred[i * (kThreadsPerCta + 1) + tid] = make_float4(ypart, gBpart, wApart, 0.f);
-        *reinterpret_cast<float4*>(&s_eB[(i * kEPW + e_w) * N + 4 * q]) =
-            make_float4(dBp[0], dBp[1], dBp[2], dBp[3]);
-        *reinterpret_cast<float4*>(&s_eC[(i * kEPW + e_w) * N + 4 * q]) =
-            make_float4(dCp[0], dCp[1], dCp[2], dCp[3]);
-      }
-      __syncwarp();
-      // sums over n: lane q finishes the timesteps i == q (mod kLPE) of the window
-      for (int i = q; i < kWin; i += kLPE) {
-        const int t = w * kWin + i;
-        float ys = 0.f, gBs = 0.f, wAs = 0.f;
-#pragma unroll
-        for (int k = 0; k < kLPE; ++k) {
-          const float4 v = s_nred[i * (kThreadsPerCta + 1) + tid - q + k];
-          ys += v.x; gBs += v.y; wAs += v.z;
-        }
-        const float4 in = s_in[(buf * kChunk + t) * kTE + e_l];     // delta, delta*x, dy', x
-        const float4 ep = s_ep[(buf * kChunk + t) * kTE + e_l];     // z, dy, dsoftplus
-        const float dxv = fmaf(in.z, Dv, in.x * gBs);
-        float ddv = fmaf(in.w, gBs, wAs * (1.f / kLog2e));
-        ddv *= ep.z;
-        dDacc = fmaf(in.z, in.w, dDacc);
-        dbias_acc += ddv;
-        s_out[(0 * kChunk + t) * kTE + e_l] = dxv;
-        s_out[(1 * kChunk + t) * kTE + e_l] = ddv;
-        if (has_z) {
-          const float sg = sigmoidf(ep.x);
-          const float yv = fmaf(Dv, in.w, ys);
-          s_out[(2 * kChunk + t) * kTE + e_l] = ep.y * yv * sg * (1.f + ep.x * (1.f - sg));
-        }
-      }
-      // sums over the warp's channels: one float4 group (timestep, B|C, n/4) per step
-      for (int g = lane; g < kWin * 2 * (N / 4); g += 32) {
-        const int i = g / (2 * (N / 4)), r = g % (2 * (N / 4));
-        const bool isC = r >= N / 4;
-        const int n4 = isC ? r - N / 4 : r;
-        const float* src = (isC ? s_eC : s_eB) + i * kEPW * N + 4 * n4;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int k = 0; k < kEPW; ++k) {
-          const float4 v = *reinterpret_cast<const float4*>(src + k * N);
-          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        }
-        float* dst = s_acc + ((isC ? 1 : 0) * kChunk + w * kWin + i) * N + 4 * n4;
-        atomicAdd(dst + 0, acc.x); atomicAdd(dst + 1, acc.y);
-        atomicAdd(dst + 2, acc.z); atomicAdd(dst + 3, acc.w);
-      }
-      __syncwarp();
-    }
-    __syncthreads();
-
-    // ---- write the chunk's dx, ddelta, dz tiles and flush its dB, dC block
-    {
-      const int rows_ok = int(min64(kChunk, p.L - t0));
-#pragma unroll
-      for (int i = 0; i < ActRegs::Map::kPerThread; ++i) {
-        if (!ActRegs::Map::owns(i, tid)) continue;
-        const int rr = ActRegs::Map::row(i, tid), cc = ActRegs::Map::col(i, tid);
-        if (rr >= rows_ok || cc >= cols_ok) continue;
-        TVec<T, KV> vx, vd, vz;
-#pragma unroll
-        for (int k = 0; k < KV; ++k) {
-          vx.v[k] = Elem<T>::from_f(s_out[(0 * kChunk + rr) * kTE + cc + k]);
-          vd.v[k] = Elem<T>::from_f(s_out[(1 * kChunk + rr) * kTE + cc + k]);
-          if (has_z) vz.v[k] = Elem<T>::from_f(s_out[(2 * kChunk + rr) * kTE + cc + k]);
-        }
-        tvec_store<T, KV>(odx + (t0 + rr) * p.dx_sl + cc, vx);
-        tvec_store<T, KV>(odd + (t0 + rr) * p.dd_sl + cc, vd);
-        if (has_z) tvec_store<T, KV>(odz + (t0 + rr) * p.dz_sl + cc, vz);
-      }
-      for (int i = tid; i < 2 * kChunk * N; i += kThreadsPerCta) {
-        const int which = i / (kChunk * N), rr = (i / N) % kChunk, n = i % N;
-        const float v = s_acc[i];
-        s_acc[i] = 0.f;
-        if (rr < rows_ok)
-          atomicAdd((which ? p.dC : p.dB) + (b * p.L + t0 + rr) * N + n, v);
-      }
-    }
-    if (c > 0) commit(buf ^ 1, t0 - kChunk);
-    __syncthreads();
-  }
-
-  // ---- sums over (b, t) kept per thread: dA, dD, d(delta_bias); and the outgoing carry
-  if (e_ok) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-      atomicAdd(p.dA + e * N + 4 * q + j, dAacc[j]);
-    if (p.g_out) {
-      *reinterpret_cast<float4*>(p.g_out + (b * p.ED + e) * N + 4 * q) =
-          make_float4(gc[0], gc[1], gc[2], gc[3]);
-    }
-  }
-#pragma unroll
-  for (int s = kLPE / 2; s >= 1; s >>= 1) {
-    dDacc += __shfl_xor_sync(0xffffffffu, dDacc, s);
-    dbias_acc += __shfl_xor_sync(0xffffffffu, dbias_acc, s);
-  }
-  if (e_ok && q == 0) {
-    if (p.dD) atomicAdd(p.dD + e, dDacc);
-    if (p.ddelta_bias) atomicAdd(p.ddelta_bias + e, dbias_acc);
-  }
-}
-
-template <typename T, int N>
-int launch_n(const SscanBwdParams& p, bool vec, cudaStream_t st) {
-  using G = SscanGeom<N>;
-  using S = BwdSmem<T, N>;
-  dim3 grid(unsigned((p.ED + G::kTE - 1) / G::kTE), unsigned(p.B));
-  constexpr int KV = Elem<T>::kVec;
-  auto kv = sscan_bwd_kernel<T, N, KV>;
-  auto k1 = sscan_bwd_kernel<T, N, 1>;
-  auto k = vec ? kv : k1;
-  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess)
-    return MB200_ELAUNCH;
-  k<<<grid, kThreadsPerCta, S::kBytes, st>>>(p);
-  return check_launch();
+__device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
+  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
 }
 
 template <typename T>
-int launch_t(const SscanBwdParams& p, int N, bool vec, cudaStream_t st) {
-  switch (N) {
-    case 8: return launch_n<T, 8>(p, vec, st);
-    case 16: return launch_n<T, 16>(p, vec, st);
-    case 32: return launch_n<T, 32>(p, vec, st);
-    case 64: return launch_n<T, 64>(p, vec, st);
-    default: return MB200_ENSTATE;
+__global__ void __launch_bounds__(kBwdThreads, 3)
+sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams p) {
+  using S = TmaBwdSmem<T>;
+  constexpr int kStages = S::kStages, kAhead = S::kStages - 2;
+  constexpr int N = kBN;
+
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  float2* s_op = reinterpret_cast<float2*>(smem_raw + S::kOp);
+  float* s_dyp = reinterpret_cast<float*>(smem_raw + S::kDyp);
+  float* s_B = reinterpret_cast<float*>(smem_raw + S::kB);
+  float* s_C = reinterpret_cast<float*>(smem_raw + S::kC);
+  float4* s_np = reinterpret_cast<float4*>(smem_raw + S::kNp);
+  float4* s_ep = reinterpret_cast<float4*>(smem_raw + S::kEp);
+  float* s_D = reinterpret_cast<float*>(smem_raw + S::kD);
+  float* s_bias = reinterpret_cast<float*>(smem_raw + S::kBias);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + S::kBars);
+  uint64_t* raw_full = bars;                      // [kStages] copy landed
+  uint64_t* raw_free = bars + kStages;            // [kStages] warps 4, 5, 7 are done with the stage
+  uint64_t* op_full = bars + 2 * kStages;         // [2] operands committed (warp 4)
+  uint64_t* op_empty = op_full + 2;               // [2] consumers are done with the operand buffer
+  uint64_t* win_full = op_full + 4;               // [2] consumers filled a window of partials
+  uint64_t* win_empty = op_full + 6;              // [2] finishing warps drained it
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t e0 = int64_t(blockIdx.x) * kBTE;
+  const int64_t b = blockIdx.y;
+  const int cols_ok = int(min64(kBTE, p.ED - e0));
+  const bool softplus = (p.flags & MB200_DELTA_SOFTPLUS) != 0;
+  const bool has_z = p.z != nullptr;
+  const int64_t ntiles = (p.L + kBTile - 1) / kBTile;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < kStages; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_free[i], 96); }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&op_full[i], 32); mbar_init(&op_empty[i], 128);
+      mbar_init(&win_full[i], 128); mbar_init(&win_empty[i], 64);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = tid; i < kBTE; i += kBwdThreads) {
+    const bool ok = i < cols_ok;
+    s_D[i] = (ok && p.D) ? p.D[e0 + i] : 0.f;
+    s_bias[i] = (ok && softplus) ? p.delta_bias[e0 + i] : 0.f;
+  }
+  __syncthreads();
+  auto fail = [&]() { atomicExch(&g_bwd_status, MB200_DEV_WAIT_TIMEOUT); };
+
+  if (warp < 4) {
+    // ================================================================== consumers
+    const int e_l = tid >> 2, q = tid & 3;
+    const int64_t e = e0 + e_l;
+    const bool e_ok = e < p.ED;
+    float2 A2[2], gc[2], dAacc[2];
+    {
+      float a4[4], g4[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        a4[j] = e_ok ? p.A[e * N + 4 * q + j] * kLog2e : 0.f;
+        g4[j] = (e_ok && p.g_in) ? p.g_in[(b * p.ED + e) * N + 4 * q + j] : 0.f;
+      }
+      A2[0] = make_float2(a4[0], a4[1]); A2[1] = make_float2(a4[2], a4[3]);
+      gc[0] = make_float2(g4[0], g4[1]); gc[1] = make_float2(g4[2], g4[3]);
+      dAacc[0] = dAacc[1] = make_float2(0.f, 0.f);
+    }
+    const int op_off0 = op_index(0, e_l, kBTE), op_off1 = op_index(1, e_l, kBTE) - kBTE;
+    const int npo = np_slot(tid);
+    const float* carry_base = p.carries + (b * ntiles * p.ED + e) * N + 4 * q;
+    auto load_carry = [&](int64_t kt) {
+      return e_ok ? *reinterpret_cast<const float4*>(carry_base + kt * p.ED * N) : make_float4(0.f, 0.f, 0.f, 0.f);
+    };
+    float4 carry_next = load_carry(ntiles - 1);
+
+    for (int64_t j = 0; j < ntiles; ++j) {
+      const int64_t kt = ntiles - 1 - j;
+      const int buf = int(j & 1);
+      const float4 cv = carry_next;
+      if (kt > 0) carry_next = load_carry(kt - 1);
+      if (!mbar_wait(&op_full[buf], int((j >> 1) & 1))) { fail(); return; }
+      const float2* op = s_op + buf * kBTile * kBTE;
+      const float* dyp = s_dyp + buf * kBTile * kBTE + e_l;
+      const float* sB = s_B + buf * kBTile * N + 4 * q;
+      const float* sC = s_C + buf * kBTile * N + 4 * q;
+      const float2 hp[2] = {make_float2(cv.x, cv.y), make_float2(cv.z, cv.w)};   // state entering the tile
+
+      // one forward step of the recurrence from operands in shared memory
+      auto step = [&](int t, float2 (&h)[2]) {
+        const float2 o = op[t * kBTE + ((t & 1) ? op_off1 : op_off0)];
+        const float4 Bq = *reinterpret_cast<const float4*>(sB + t * N);
+        const float2 dd = make_float2(o.x, o.x), dxx = make_float2(o.y, o.y);
+        const float2 e0v = __fmul2_rn(dd, A2[0]), e1v = __fmul2_rn(dd, A2[1]);
+        const float2 a0 = make_float2(ex2f(e0v.x), ex2f(e0v.y)), a1 = make_float2(ex2f(e1v.x), ex2f(e1v.y));
+        h[0] = __ffma2_rn(a0, h[0], __fmul2_rn(dxx, make_float2(Bq.x, Bq.y)));
+        h[1] = __ffma2_rn(a1, h[1], __fmul2_rn(dxx, make_float2(Bq.z, Bq.w)));
+      };
+
+      float2 hmid[2] = {hp[0], hp[1]};
+#pragma unroll
+      for (int t = 0; t < kHalf; ++t) step(t, hmid);          // state entering the second half
+
+#pragma unroll
+      for (int half = 1; half >= 0; --half) {
+        // states after each step of this half, in registers
+        float2 hh[kHalf][2];
+        {
+          float2 h[2] = {half ? hmid[0] : hp[0], half ? hmid[1] : hp[1]};
+#pragma unroll
+          for (int i = 0; i < kHalf; ++i) {
+            step(half * kHalf + i, h);
+            hh[i][0] = h[0]; hh[i][1] = h[1];
+          }
+        }
+#pragma unroll
+        for (int wi = kHalf / kBWin - 1; wi >= 0; --wi) {
+          // window sequence number: tiles in processing order, windows from the tile's end
+          const int64_t wseq = j * kWinsPerTile + (1 - half) * (kHalf / kBWin) + (kHalf / kBWin - 1 - wi);
+          const int wb = int(wseq & 1);
+          if (wseq >= 2 && !mbar_wait(&win_empty[wb], int(((wseq - 2) >> 1) & 1))) { fail(); return; }
+          float4* np = s_np + wb * kBWin * 128;
+          float4* ep = s_ep + wb * kBWin * 2 * 4 * kEpStride;
+#pragma unroll
+          for (int ti = kBWin - 1; ti >= 0; --ti) {
+            const int i = wi * kBWin + ti;                    // index inside the half
+            const int t = half * kHalf + i;                   // index inside the tile
+            const float2 o = op[t * kBTE + ((t & 1) ? op_off1 : op_off0)];
+            const float dyv = dyp[t * kBTE];
+            const float4 Bq = *reinterpret_cast<const float4*>(sB + t * N);
+            const float4 Cq = *reinterpret_cast<const float4*>(sC + t * N);
+            const float2 dd = make_float2(o.x, o.x), dxx = make_float2(o.y, o.y), dy2 = make_float2(dyv, dyv);
+            const float2 Bv[2] = {make_float2(Bq.x, Bq.y), make_float2(Bq.z, Bq.w)};
+            const float2 Cv[2] = {make_float2(Cq.x, Cq.y), make_float2(Cq.z, Cq.w)};
+            float2 ysum = make_float2(0.f, 0.f), gBs = ysum, wAs = ysum;
+            float2 dBp[2], dCp[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+              const float2 ev = __fmul2_rn(dd, A2[k]);
+              const float2 a = make_float2(ex2f(ev.x), ex2f(ev.y));
+              const float2 hcur = hh[i][k];
+              const float2 hprev = i ? hh[i - 1][k] : (half ? hmid[k] : hp[k]);
+              const float2 g = __ffma2_rn(dy2, Cv[k], gc[k]);
+              ysum = __ffma2_rn(hcur, Cv[k], ysum);
+              dCp[k] = __fmul2_rn(dy2, hcur);
+              dBp[k] = __fmul2_rn(g, dxx);
+              gBs = __ffma2_rn(g, Bv[k], gBs);
+              const float2 w = __fmul2_rn(__fmul2_rn(g, hprev), a);
+              dAacc[k] = __ffma2_rn(w, dd, dAacc[k]);
+              wAs = __ffma2_rn(w, A2[k], wAs);
+              gc[k] = __fmul2_rn(a, g);
+            }
+            np[ti * 128 + npo] = make_float4(ysum.x + ysum.y, gBs.x + gBs.y, wAs.x + wAs.y, 0.f);
+            ep[((ti * 2 + 0) * 4 + q) * kEpStride + e_l] = make_float4(dBp[0].x, dBp[0].y, dBp[1].x, dBp[1].y);
+            ep[((ti * 2 + 1) * 4 + q) * kEpStride + e_l] = make_float4(dCp[0].x, dCp[0].y, dCp[1].x, dCp[1].y);
+          }
+          mbar_arrive(&win_full[wb]);
+        }
+      }
+      mbar_arrive(&op_empty[buf]);
+    }
+    if (e_ok) {
+      float* dA = p.dA + e * N + 4 * q;
+      atomicAdd(dA + 0, dAacc[0].x); atomicAdd(dA + 1, dAacc[0].y);
+      atomicAdd(dA + 2, dAacc[1].x); atomicAdd(dA + 3, dAacc[1].y);
+      if (p.g_out)
+        *reinterpret_cast<float4*>(p.g_out + (b * p.ED + e) * N + 4 * q) =
+            make_float4(gc[0].x, gc[0].y, gc[1].x, gc[1].y);
+    }
+    return;
+  }
+  auto stage_ptr = [&](int64_t j) { return smem_raw + S::kRaw + int(j % kStages) * S::kStageBytes; };
+  // window wl (0..7, in processing order) of a tile covers timesteps win_t(wl) and win_t(wl) + 1
+  auto win_t = [](int wl) { return (wl < 4 ? kHalf : 0) + 2 * (3 - (wl & 3)); };
+
+  if (warp == 4) {
+    // ================================================================== loader + converter
+    const uint32_t stage_tx = uint32_t((has_z ? 4 : 3) * S::kActBytes + 2 * S::kBcBytes);
+    auto issue = [&](int64_t j) -> bool {                       // lane 0 only
+      const int r = int(j % kStages);
+      if (j >= kStages && !mbar_wait(&raw_free[r], int((j / kStages - 1) & 1))) return false;
+      unsigned char* st = stage_ptr(j);
+      const int t0 = int((ntiles - 1 - j) * kBTile);
+      mbar_expect_tx(&raw_full[r], stage_tx);
+      tma_load_3d(st, &maps.x, int(e0), t0, int(b), &raw_full[r]);
+      tma_load_3d(st + S::kActBytes, &maps.d, int(e0), t0, int(b), &raw_full[r]);
+      if (has_z) tma_load_3d(st + 2 * S::kActBytes, &maps.z, int(e0), t0, int(b), &raw_full[r]);
+      tma_load_3d(st + 3 * S::kActBytes, &maps.dy, int(e0), t0, int(b), &raw_full[r]);
+      tma_load_3d(st + 4 * S::kActBytes, &maps.B, 0, t0, int(b), &raw_full[r]);
+      tma_load_3d(st + 4 * S::kActBytes + S::kBcBytes, &maps.C, 0, t0, int(b), &raw_full[r]);
+      return true;
+    };
+    if (lane == 0) {
+      for (int64_t j = 0; j < kAhead && j < ntiles; ++j)
+        if (!issue(j)) { fail(); return; }
+    }
+    for (int64_t j = 0; j < ntiles; ++j) {
+      const int buf = int(j & 1);
+      const int rows_ok = int(min64(kBTile, p.L - (ntiles - 1 - j) * kBTile));
+      if (j >= 2 && !mbar_wait(&op_empty[buf], int(((j - 2) >> 1) & 1))) { fail(); return; }
+      if (!mbar_wait(&raw_full[j % kStages], int((j / kStages) & 1))) { fail(); return; }
+      const unsigned char* st = stage_ptr(j);
+      const T* rx = reinterpret_cast<const T*>(st);
+      const T* rd = reinterpret_cast<const T*>(st + S::kActBytes);
+      const T* rz = reinterpret_cast<const T*>(st + 2 * S::kActBytes);
+      const T* rdy = reinterpret_cast<const T*>(st + 3 * S::kActBytes);
+      float2* tile = s_op + buf * kBTile * kBTE;
+      float* dyt = s_dyp + buf * kBTile * kBTE;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int v = lane + 32 * i;
+        const int rr = v >> 3, cc = (v & 7) * 4;
+        const Vec4<T> xv = *reinterpret_cast<const Vec4<T>*>(rx + rr * kBTE + cc);
+        const Vec4<T> dv4 = *reinterpret_cast<const Vec4<T>*>(rd + rr * kBTE + cc);
+        const Vec4<T> yv4 = *reinterpret_cast<const Vec4<T>*>(rdy + rr * kBTE + cc);
+        Vec4<T> zv4 = yv4;
+        if (has_z) zv4 = *reinterpret_cast<const Vec4<T>*>(rz + rr * kBTE + cc);
+        float2 o[4];
+        float dyo[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float dv = Elem<T>::to_f(dv4.v[k]);
+          if (softplus) dv = softplus_fast(dv + s_bias[cc + k]);
+          if (rr >= rows_ok) dv = 0.f;
+          o[k] = make_float2(dv, dv * Elem<T>::to_f(xv.v[k]));
+          float g = Elem<T>::to_f(yv4.v[k]);
+          if (has_z) {
+            const float zf = Elem<T>::to_f(zv4.v[k]);
+            g *= zf * sigmoid_fast(zf);
+          }
+          dyo[k] = g;
+        }
+        *reinterpret_cast<float4*>(tile + op_index(rr, cc, kBTE)) = make_float4(o[0].x, o[0].y, o[1].x, o[1].y);
+        *reinterpret_cast<float4*>(tile + op_index(rr, cc + 2, kBTE)) = make_float4(o[2].x, o[2].y, o[3].x, o[3].y);
+        *reinterpret_cast<float4*>(dyt + rr * kBTE + cc) = make_float4(dyo[0], dyo[1], dyo[2], dyo[3]);
+      }
+      const T* rB = reinterpret_cast<const T*>(st + 4 * S::kActBytes);      // B box then C box
+      float* dstB = s_B + buf * kBTile * N;
+      float* dstC = s_C + buf * kBTile * N;
+      constexpr int kBcVecs = kBTile * N / 4;                                // 64
+#pragma unroll
+      for (int i = 0; i < 2 * kBcVecs / 32; ++i) {
+        const int v = lane + 32 * i;
+        const Vec4<T> r4 = *reinterpret_cast<const Vec4<T>*>(rB + v * 4);
+        float* dst = (v < kBcVecs) ? dstB + v * 4 : dstC + (v - kBcVecs) * 4;
+        *reinterpret_cast<float4*>(dst) = make_float4(Elem<T>::to_f(r4.v[0]), Elem<T>::to_f(r4.v[1]),
+                                                      Elem<T>::to_f(r4.v[2]), Elem<T>::to_f(r4.v[3]));
+      }
+      mbar_arrive(&op_full[buf]);
+      mbar_arrive(&raw_free[j % kStages]);
+      if (lane == 0 && j + kAhead < ntiles && !issue(j + kAhead)) { fail(); return; }
+    }
+    return;
+  }
+
+  if (warp == 6) {
+    // ================================================================== dB, dC: sums over channels
+    const int ti = lane >> 4, which = (lane >> 3) & 1, qq = (lane >> 1) & 3, hf = lane & 1;
+    float* gbase = (which ? p.dC : p.dB) + b * p.L * N + 4 * qq + 2 * hf;
+    for (int64_t j = 0; j < ntiles; ++j) {
+      const int64_t t0 = (ntiles - 1 - j) * kBTile;
+#pragma unroll 1
+      for (int wl = 0; wl < kWinsPerTile; ++wl) {
+        const int64_t wseq = j * kWinsPerTile + wl;
+        const int wb = int(wseq & 1);
+        if (!mbar_wait(&win_full[wb], int((wseq >> 1) & 1))) { fail(); return; }
+        const float* src = reinterpret_cast<const float*>(
+                               s_ep + wb * kBWin * 2 * 4 * kEpStride + ((ti * 2 + which) * 4 + qq) * kEpStride) + 2 * hf;
+        float2 acc0 = make_float2(0.f, 0.f), acc1 = acc0;
+#pragma unroll
+        for (int k = 0; k < kBTE; k += 2) {
+          acc0 = __fadd2_rn(acc0, *reinterpret_cast<const float2*>(src + 4 * k));
+          acc1 = __fadd2_rn(acc1, *reinterpret_cast<const float2*>(src + 4 * (k + 1)));
+        }
+        mbar_arrive(&win_empty[wb]);
+        const int64_t t = t0 + win_t(wl) + ti;
+        if (t < p.L) red_add_v2(gbase + t * N, acc0.x + acc1.x, acc0.y + acc1.y);
+      }
+    }
+    return;
+  }
+
+  // ==================================================================== warps 5, 7: dx, ddelta, dz
+  {
+    const int par = (warp == 5) ? 0 : 1;                 // parity of the windows this warp finishes
+    const int ti = lane >> 4, c0 = (lane & 15) * 2;
+    T* odx = static_cast<T*>(p.dx) + b * p.dx_sb + e0 + c0;
+    T* odd = static_cast<T*>(p.ddelta) + b * p.dd_sb + e0 + c0;
+    T* odz = has_z ? static_cast<T*>(p.dz) + b * p.dz_sb + e0 + c0 : nullptr;
+    const float Dv[2] = {s_D[c0], s_D[c0 + 1]};
+    const float bv[2] = {s_bias[c0], s_bias[c0 + 1]};
+    float dDacc[2] = {0.f, 0.f}, dbacc[2] = {0.f, 0.f};
+    for (int64_t j = 0; j < ntiles; ++j) {
+      const int64_t t0 = (ntiles - 1 - j) * kBTile;
+      if (!mbar_wait(&raw_full[j % kStages], int((j / kStages) & 1))) { fail(); return; }
+      const unsigned char* st = stage_ptr(j);
+      const T* rx = reinterpret_cast<const T*>(st);
+      const T* rd = reinterpret_cast<const T*>(st + S::kActBytes);
+      const T* rz = reinterpret_cast<const T*>(st + 2 * S::kActBytes);
+      const T* rdy = reinterpret_cast<const T*>(st + 3 * S::kActBytes);
+#pragma unroll 1
+      for (int wl = par; wl < kWinsPerTile; wl += 2) {
+        const int64_t wseq = j * kWinsPerTile + wl;
+        if (!mbar_wait(&win_full[par], int((wseq >> 1) & 1))) { fail(); return; }
+        const float4* np = s_np + par * kBWin * 128 + ti * 128;
+        float ys[2], gBs[2], wAs[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          ys[k] = gBs[k] = wAs[k] = 0.f;
+#pragma unroll
+          for (int qi = 0; qi < 4; ++qi) {
+            const float4 v = np[np_slot((c0 + k) * 4 + qi)];
+            ys[k] += v.x; gBs[k] += v.y; wAs[k] += v.z;
+          }
+        }
+        mbar_arrive(&win_empty[par]);
+        const int tt = win_t(wl) + ti;                   // timestep inside the tile
+        const int64_t t = t0 + tt;
+        if (t < p.L && c0 < cols_ok) {
+          const Vec2<T> xv = *reinterpret_cast<const Vec2<T>*>(rx + tt * kBTE + c0);
+          const Vec2<T> dv2 = *reinterpret_cast<const Vec2<T>*>(rd + tt * kBTE + c0);
+          const Vec2<T> yv2 = *reinterpret_cast<const Vec2<T>*>(rdy + tt * kBTE + c0);
+          Vec2<T> zv2 = yv2;
+          if (has_z) zv2 = *reinterpret_cast<const Vec2<T>*>(rz + tt * kBTE + c0);
+          Vec2<T> ox, od, oz;
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const float xf = Elem<T>::to_f(xv.v[k]), dyf = Elem<T>::to_f(yv2.v[k]);
+            float dv = Elem<T>::to_f(dv2.v[k]), spg = 1.f;
+            if (softplus) {
+              const float raw = dv + bv[k];
+              dv = softplus_fast(raw);
+              spg = sigmoid_fast(raw);
+            }
+            float dyg = dyf, dzv = 0.f;
+            if (has_z) {
+              const float zf = Elem<T>::to_f(zv2.v[k]);
+              const float sg = sigmoid_fast(zf);
+              dyg = dyf * zf * sg;
+              dzv = dyf * fmaf(Dv[k], xf, ys[k]) * sg * (1.f + zf * (1.f - sg));
+            }
+            const float dxv = fmaf(dyg, Dv[k], dv * gBs[k]);
+            const float ddv = fmaf(xf, gBs[k], wAs[k] * (1.f / kLog2e)) * spg;
+            if (c0 + k < cols_ok) {
+              dDacc[k] = fmaf(dyg, xf, dDacc[k]);
+              dbacc[k] += ddv;
+            }
+            ox.v[k] = Elem<T>::from_f(dxv);
+            od.v[k] = Elem<T>::from_f(ddv);
+            oz.v[k] = Elem<T>::from_f(dzv);
+          }
+          if (c0 + 2 <= cols_ok) {
+            *reinterpret_cast<Vec2<T>*>(odx + t * p.dx_sl) = ox;
+            *reinterpret_cast<Vec2<T>*>(odd + t * p.dd_sl) = od;
+            if (has_z) *reinterpret_cast<Vec2<T>*>(odz + t * p.dz_sl) = oz;
+          } else {
+            odx[t * p.dx_sl] = ox.v[0];
+            odd[t * p.dd_sl] = od.v[0];
+            if (has_z) odz[t * p.dz_sl] = oz.v[0];
+          }
+        }
+      }
+      mbar_arrive(&raw_free[j % kStages]);
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      if (c0 + k < cols_ok) {
+        if (p.dD) atomicAdd(p.dD + e0 + c0 + k, dDacc[k]);
+        if (p.ddelta_bias) atomicAdd(p.ddelta_bias + e0 + c0 + k, dbacc[k]);
+      }
+    }
   }
 }
 
 }  // namespace
 }  // namespace mb200
 
+namespace mb200 {
+namespace {
+
+template <typename T>
+int bwd_tma_launch(const SscanBwdParams& p, cudaStream_t st) {
+  using S = TmaBwdSmem<T>;
+  constexpr bool bf = sizeof(T) == 2;
+  BwdMaps m;
+  bool ok = tma_encode(&m.x, p.x, bf, p.B, p.L, p.ED, p.x_sb, p.x_sl, kBTE, kBTile) &&
+            tma_encode(&m.d, p.delta, bf, p.B, p.L, p.ED, p.d_sb, p.d_sl, kBTE, kBTile) &&
+            tma_encode(&m.dy, p.dy, bf, p.B, p.L, p.ED, p.dy_sb, p.dy_sl, kBTE, kBTile) &&
+            tma_encode(&m.B, p.Bm, bf, p.B, p.L, kBN, p.b_sb, p.b_sl, kBN, kBTile) &&
+            tma_encode(&m.C, p.Cm, bf, p.B, p.L, kBN, p.c_sb, p.c_sl, kBN, kBTile);
+  if (ok && p.z) ok = tma_encode(&m.z, p.z, bf, p.B, p.L, p.ED, p.z_sb, p.z_sl, kBTE, kBTile);
+  else if (ok) m.z = m.x;
+  if (!ok) return 1;                                   // caller falls back to the generic path
+  auto k = sscan_bwd_tma_kernel<T>;
+  if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess)
+    return MB200_ELAUNCH;
+  dim3 grid(unsigned((p.ED + kBTE - 1) / kBTE), unsigned(p.B));
+  k<<<grid, kBwdThreads, S::kBytes, st>>>(m, p);
+  return check_launch();
+}
+
+bool bwd_tma_path_ok(const SscanBwdParams& p, int N, int es) {
+  if (N != kBN || p.L >= (int64_t(1) << 31) || p.ED >= (int64_t(1) << 31)) return false;
+  bool ok = tma_compatible(p.x, p.x_sb, p.x_sl, p.ED, es, kBTE) &&
+            tma_compatible(p.delta, p.d_sb, p.d_sl, p.ED, es, kBTE) &&
+            tma_compatible(p.dy, p.dy_sb, p.dy_sl, p.ED, es, kBTE) &&
+            tma_compatible(p.Bm, p.b_sb, p.b_sl, N, es, N) &&
+            tma_compatible(p.Cm, p.c_sb, p.c_sl, N, es, N);
+  if (p.z) ok = ok && tma_compatible(p.z, p.z_sb, p.z_sl, p.ED, es, kBTE) && aligned16(p.dz) &&
+                (p.dz_sl * es) % 16 == 0 && (p.dz_sb * es) % 16 == 0;
+  ok = ok && aligned16(p.dx) && aligned16(p.ddelta) && (p.dx_sl * es) % 16 == 0 && (p.dx_sb * es) % 16 == 0 &&
+       (p.dd_sl * es) % 16 == 0 && (p.dd_sb * es) % 16 == 0 && aligned16(p.dB) && aligned16(p.dC);
+  return ok && tma_encoder() != nullptr;
+}
+
+}  // namespace
+}  // namespace mb200
+
 using namespace mb200;
+
+// Reads (and clears) the device-side status word of the backward kernel.  Synchronises the device.
+int mb200_bwd_device_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_bwd_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_bwd_status, &zero, sizeof(int));
+  return v;
+}
 
 extern "C" int mb200_sscan_bwd(const void* x, const void* delta, const void* z, const float* A,
                                const void* Bm, const void* Cm, const float* D,
@@ -381,6 +537,11 @@ extern "C" int mb200_sscan_bwd(const void* x, const void* delta, const void* z, 
   p.b_sb = b_sb; p.b_sl = b_sl; p.c_sb = c_sb; p.c_sl = c_sl; p.dy_sb = dy_sb; p.dy_sl = dy_sl;
   p.dx_sb = dx_sb; p.dx_sl = dx_sl; p.dd_sb = dd_sb; p.dd_sl = dd_sl; p.dz_sb = dz_sb; p.dz_sl = dz_sl;
   p.flags = flags;
+  const int es = dtype == MB200_F32 ? 4 : 2;
+  if (bwd_tma_path_ok(p, N, es)) {
+    const int rc = dtype == MB200_F32 ? bwd_tma_launch<float>(p, st) : bwd_tma_launch<__nv_bfloat16>(p, st);
+    if (rc <= 0) return rc;
+  }
   const int kv = dtype == MB200_F32 ? 4 : 8;
   bool vec = ED % kv == 0;
   for (const void* q : {x, delta, z, Bm, Cm, dy, (const void*)dx, (const void*)ddelta, (const void*)dz})
@@ -388,5 +549,6 @@ extern "C" int mb200_sscan_bwd(const void* x, const void* delta, const void* z, 
   for (int64_t s : {x_sb, x_sl, d_sb, d_sl, b_sb, b_sl, c_sb, c_sl, dy_sb, dy_sl, dx_sb, dx_sl, dd_sb, dd_sl})
     vec = vec && s % kv == 0;
   if (z) vec = vec && z_sb % kv == 0 && z_sl % kv == 0 && dz_sb % kv == 0 && dz_sl % kv == 0;
-  return dtype == MB200_F32 ? launch_t<float>(p, N, vec, st) : launch_t<__nv_bfloat16>(p, N, vec, st);
+  return dtype == MB200_F32 ? bwd_generic_launch_t<float>(p, N, vec, st)
+                            : bwd_generic_launch_t<__nv_bfloat16>(p, N, vec, st);
 }

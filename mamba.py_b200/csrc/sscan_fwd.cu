@@ -37,11 +37,6 @@ constexpr int kTmaProducers = 128;
 constexpr int kTmaThreads = kConsumers + kTmaProducers;
 constexpr int kTile = kChunk;              // timesteps per tile (= carry spacing)
 
-// four consecutive channels of one timestep, moved with one 8- or 16-byte access
-template <typename T> struct alignas(sizeof(T) * 4) Vec4 {
-  T v[4];
-};
-
 struct FwdMaps {
   CUtensorMap x, d, z, B, C;
 };

@@ -249,4 +249,7 @@ extern "C" const char* mb200_strerror(int code) {
 
 extern "C" int mb200_version(void) { return 100; }
 
-extern "C" int mb200_device_status(void) { return mb200_fwd_device_status(); }
+extern "C" int mb200_device_status(void) {
+  const int f = mb200_fwd_device_status(), b = mb200_bwd_device_status();
+  return (f < 0 || b < 0) ? -1 : (f | b);
+}
