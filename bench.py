@@ -312,6 +312,9 @@ def bench_scan_130m(args, rank, world, dev):
                              "GBps": bwd_bytes / bwd_ms / 1e6},
     }
     res["dominant"] = ("sscan_bwd_kernel", bwd_bytes, bwd_ms)
+    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of that kernel on this exact workload,
+    # from the ncu capture summarised in profiles/sscan_bwd_kernel__scan_130m.md (306.3 MB + 126.4 MB)
+    res["traffic"] = 432.7e6
 
     if args.skip_e2e:
         sampler.stop()
@@ -477,7 +480,9 @@ def main():
         "metric": METRIC[wl], "value": res["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": res["ms_per_step"], "higher_is_better": True,
         "scaling": SCALING[wl], "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(wl, world), "roofline": roof, "kernels": res.get("kernels"),
+        "config": dict(workload_config(wl, world), **({"seq_len": res["seq_len"]} if "seq_len" in res else {}),
+                       **({"subshards_per_gpu": res["subshards"]} if "subshards" in res else {})),
+        "roofline": roof, "kernels": res.get("kernels"),
         "e2e": res.get("e2e"), "gpu_launches": res["gpu_launches"], "clocks": res.get("clocks"),
     }
     if rank == 0:

@@ -134,7 +134,7 @@ def bench_decode(args, rank, world, dev, ClockSampler, time_region, time_kernel)
 def bench_lshard(args, rank, world, dev, ClockSampler, time_region, time_kernel):
     """Long sequence split over the ranks along L; fwd+bwd with the carry exchange (strong scaling)."""
     import torch.distributed as dist
-    from .lshard import selective_scan_lsharded
+    from .lshard import selective_scan_lsharded, pick_subshards, _split
     L = int(os.environ.get("MB200_LSHARD_L", "131072"))
     Bsz, ED, N = 1, 5120, 16
     if not dist.is_initialized():
@@ -158,9 +158,13 @@ def bench_lshard(args, rank, world, dev, ClockSampler, time_region, time_kernel)
     sampler.start()
     ms, t_lo, t_hi = time_region(step, args.steps, world)
     res = {"value": Bsz * L * args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
-           "gpu_launches": 8 * args.steps}
+           "gpu_launches": 8 * args.steps, "seq_len": L}
 
-    d = {k: w[k].detach() for k in ("x", "delta", "z", "B", "C", "A", "D", "dy")}
+    # the two big kernels alone, on the sub-sharded view the sharded scan really launches
+    S = pick_subshards(Bsz, Ls, ED, world)
+    d = {k: w[k].detach() for k in ("A", "D")}
+    d.update({k: _split(w[k].detach(), S) for k in ("x", "delta", "z", "B", "C", "dy")})
+    res["subshards"] = S
     keep = {}
 
     def fwd():
@@ -191,8 +195,8 @@ def bench_lshard(args, rank, world, dev, ClockSampler, time_region, time_kernel)
     if not args.skip_e2e:
         # end to end on a bounded slice of the shard (the whole shard would pin > 10 GB of host memory)
         n = min(Ls, 16384)
-        host_in = {k: d[k][:, :n].cpu().pin_memory() for k in ("x", "delta", "z", "B", "C", "dy")}
-        dev_in = {k: torch.empty_like(d[k][:, :n]) for k in host_in}
+        host_in = {k: w[k].detach()[:, :n].cpu().pin_memory() for k in ("x", "delta", "z", "B", "C", "dy")}
+        dev_in = {k: torch.empty_like(w[k].detach()[:, :n]) for k in host_in}
         host_out = []
 
         def e2e_step():

@@ -103,34 +103,94 @@ def _gather(t: torch.Tensor, group) -> torch.Tensor:
     return out
 
 
-def sharded_forward(ops, group, x, delta, A, Bm, Cm, D, z, delta_bias, want_carries=True):
-    """Steps 1-5 of the forward.  Returns (y, h_in, P_all, carries, hT)."""
-    rank = dist.get_rank(group)
-    S = ops.carry_pass(x, delta, A, Bm, Cm, delta_bias)
-    P = ops.decay_prod(delta, A, delta_bias)
-    PS = _gather(torch.stack([P, S]), group)                  # (R, 2, B, ED, N)
-    P_all, S_all = PS[:, 0].contiguous(), PS[:, 1].contiguous()
-    h_in = ops.fold(P_all, S_all, rank, False)
-    y, hT, carries = ops.full_fwd(x, delta, A, Bm, Cm, D, z, delta_bias, h_in, want_carries)
-    return y, h_in, P_all, carries, hT
+def _split(t, S):
+    """(B, L, C) -> (B*S, L/S, C): every batch row cut into S consecutive sub-shards (a view when
+    the batch stride allows it)."""
+    if t is None or S == 1:
+        return t
+    return t.unflatten(1, (S, t.shape[1] // S)).flatten(0, 1)
 
 
-def sharded_backward(ops, group, x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, P_all):
-    """Steps 1-5 of the backward.  Returns what `full_bwd` returns, parameter grads all-reduced."""
-    rank = dist.get_rank(group)
-    G = ops.rev_carry_pass(delta, z, dy, Cm, A, delta_bias)
-    G_all = _gather(G, group)                                 # (R, B, ED, N)
-    g_in = ops.fold(P_all, G_all, rank, True)
-    outs = list(ops.full_bwd(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in))
-    # dA, dD, d(delta_bias) are sums over all timesteps: one flat all-reduce
-    parts = [outs[5].reshape(-1), outs[6].reshape(-1)] + ([outs[7].reshape(-1)] if outs[7] is not None else [])
-    flat = torch.cat(parts)
-    dist.all_reduce(flat, group=group)
-    nA, nD = outs[5].numel(), outs[6].numel()
-    outs[5] = flat[:nA].view_as(outs[5])
-    outs[6] = flat[nA:nA + nD].view_as(outs[6])
-    if outs[7] is not None:
-        outs[7] = flat[nA + nD:].view_as(outs[7])
+def _merge(t, S):
+    """Inverse of _split for outputs: (B*S, L/S, C) -> (B, L, C)."""
+    if t is None or S == 1:
+        return t
+    return t.unflatten(0, (t.shape[0] // S, S)).flatten(1, 2)
+
+
+def pick_subshards(Bsz, L_local, ED, world):
+    """How many sub-shards to cut each rank's slice into so that one GPU has enough independent
+    (batch row, channel tile) work items.  Each CTA owns 32 channels of one row and about 444 CTAs
+    are resident on a B200; with fewer items most SMs idle.  On a single rank sub-sharding costs
+    an extra carry pass, so it is only chosen when the GPU would otherwise be under half full."""
+    items = Bsz * ((ED + 31) // 32)
+    best, best_eff = 1, None
+    for S in (1, 2, 4, 8):
+        if L_local % (16 * S):
+            continue
+        n = items * S
+        eff = n / (-(-n // 444) * 444)
+        if world == 1 and S > 1:
+            eff *= 0.7                                   # the extra carry passes
+        if best_eff is None or eff > best_eff + 1e-9:
+            best, best_eff = S, eff
+    return best
+
+
+def sharded_forward(ops, group, x, delta, A, Bm, Cm, D, z, delta_bias, want_carries=True, subshards=1):
+    """Steps 1-5 of the forward.  Returns (y, h_in, P_all, carries, hT).
+
+    With subshards = S > 1 every rank's slice is itself cut into S consecutive pieces that are
+    scanned as extra batch rows; the fold then runs over the R*S pieces in sequence order.
+    h_in is (B*S, ED, N): the state entering each piece.  P_all is (R*S, B, ED, N)."""
+    rank, R, S = dist.get_rank(group), dist.get_world_size(group), subshards
+    Bsz = x.shape[0]
+    xs, ds, zs, Bs, Cs = (_split(t, S) for t in (x, delta, z, Bm, Cm))
+    if R * S == 1:
+        y, hT, carries = ops.full_fwd(xs, ds, A, Bs, Cs, D, zs, delta_bias, None, want_carries)
+        return y, None, None, carries, hT
+    Sl = ops.carry_pass(xs, ds, A, Bs, Cs, delta_bias)                     # (B*S, ED, N)
+    P = ops.decay_prod(ds, A, delta_bias)
+    PS = torch.stack([P, Sl]).unflatten(1, (Bsz, S))                       # (2, B, S, ED, N)
+    PS = _gather(PS, group) if R > 1 else PS.unsqueeze(0)                  # (R, 2, B, S, ED, N)
+    PS = PS.permute(1, 0, 3, 2, 4, 5).reshape(2, R * S, Bsz, *P.shape[1:]).contiguous()
+    P_all, S_all = PS[0], PS[1]                                            # (R*S, B, ED, N)
+    h_in = torch.stack([ops.fold(P_all, S_all, rank * S + s, False) for s in range(S)], dim=1)
+    h_in = h_in.flatten(0, 1).contiguous()                                 # (B*S, ED, N)
+    y, hT, carries = ops.full_fwd(xs, ds, A, Bs, Cs, D, zs, delta_bias, h_in, want_carries)
+    hT = hT.unflatten(0, (Bsz, S))[:, -1]
+    return _merge(y, S), h_in, P_all, carries, hT
+
+
+def sharded_backward(ops, group, x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, P_all, subshards=1):
+    """Steps 1-5 of the backward.  Returns what `full_bwd` returns (per-token gradients merged back
+    to (B, L/R, .), parameter gradients all-reduced; the last entry is the carry leaving the slice)."""
+    rank, R, S = dist.get_rank(group), dist.get_world_size(group), subshards
+    Bsz = x.shape[0]
+    xs, ds, zs, Bs, Cs, dys = (_split(t, S) for t in (x, delta, z, Bm, Cm, dy))
+    if R * S == 1:
+        g_in = None
+    else:
+        G = ops.rev_carry_pass(ds, zs, dys, Cs, A, delta_bias).unflatten(0, (Bsz, S))   # (B, S, ED, N)
+        G = _gather(G, group) if R > 1 else G.unsqueeze(0)                               # (R, B, S, ED, N)
+        G_all = G.permute(0, 2, 1, 3, 4).reshape(R * S, Bsz, *G.shape[3:]).contiguous()
+        g_in = torch.stack([ops.fold(P_all, G_all, rank * S + s, True) for s in range(S)], dim=1)
+        g_in = g_in.flatten(0, 1).contiguous()
+    outs = list(ops.full_bwd(xs, ds, A, Bs, Cs, D, zs, delta_bias, dys, carries, g_in))
+    for i in range(5):
+        outs[i] = _merge(outs[i], S)
+    if outs[8] is not None and S > 1:
+        outs[8] = outs[8].unflatten(0, (Bsz, S))[:, 0]
+    if R > 1:
+        # dA, dD, d(delta_bias) are sums over all timesteps: one flat all-reduce
+        parts = [outs[5].reshape(-1), outs[6].reshape(-1)] + ([outs[7].reshape(-1)] if outs[7] is not None else [])
+        flat = torch.cat(parts)
+        dist.all_reduce(flat, group=group)
+        nA, nD = outs[5].numel(), outs[6].numel()
+        outs[5] = flat[:nA].view_as(outs[5])
+        outs[6] = flat[nA:nA + nD].view_as(outs[6])
+        if outs[7] is not None:
+            outs[7] = flat[nA + nD:].view_as(outs[7])
     return tuple(outs)
 
 
@@ -143,9 +203,10 @@ class LShardSelectiveScanFn(torch.autograd.Function):
         Bs, Cs = _rows(Bm, dt), _rows(Cm, dt)
         A32, D32, b32 = _f32(A), _f32(D), _f32(delta_bias)
         needs_grad = any(t is not None and t.requires_grad for t in (x, delta, A, Bm, Cm, D, z, delta_bias))
+        S = pick_subshards(xs.shape[0], xs.shape[1], xs.shape[2], dist.get_world_size(group))
         y, h_in, P_all, carries, _ = sharded_forward(CudaOps, group, xs, ds, A32, Bs, Cs, D32, zs, b32,
-                                                     want_carries=needs_grad)
-        ctx.group = group
+                                                     want_carries=needs_grad, subshards=S)
+        ctx.group, ctx.subshards = group, S
         ctx.save_for_backward(xs, ds, A32, Bs, Cs, D32, zs, b32, carries, P_all)
         ctx.in_dtypes = tuple(None if t is None else t.dtype for t in (x, delta, A, Bm, Cm, D, z, delta_bias))
         return y
@@ -155,7 +216,7 @@ class LShardSelectiveScanFn(torch.autograd.Function):
         xs, ds, A32, Bs, Cs, D32, zs, b32, carries, P_all = ctx.saved_tensors
         dy = _rows(dy, xs.dtype)
         dx, dd, dz, dB, dC, dA, dD, dbias, _ = sharded_backward(
-            CudaOps, ctx.group, xs, ds, A32, Bs, Cs, D32, zs, b32, dy, carries, P_all)
+            CudaOps, ctx.group, xs, ds, A32, Bs, Cs, D32, zs, b32, dy, carries, P_all, subshards=ctx.subshards)
         tx, td, tA, tB, tC, tD, tz, tb = ctx.in_dtypes
         cast = lambda g, t: None if (g is None or t is None) else g.to(t)
         return (cast(dx, tx), cast(dd, td), cast(dA, tA), cast(dB, tB), cast(dC, tC), cast(dD, tD),

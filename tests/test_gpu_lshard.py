@@ -79,6 +79,30 @@ def test_sharded_equals_unsharded_kernel_long_bf16():
         assert_close(got[k], ref, 1e-3, 1e-3 * ref.abs().max().item(), k)
 
 
+def test_single_rank_subsharded_matches_oracle():
+    """One rank, one long row: the slice is cut into sub-shards scanned as batch rows."""
+    import torch.distributed as dist
+    from mamba_b200.lshard import selective_scan_lsharded, pick_subshards
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()))
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device(DEV))
+    try:
+        inp = scan_inputs(91, 1, 512, 64, 16, structured_A=False, big_delta=True)
+        assert pick_subshards(1, 512, 64, 1) > 1
+        lv = {k: inp[k].to(DEV).requires_grad_() for k in ("x", "delta", "z", "B", "C", "A", "D")}
+        y = selective_scan_lsharded(lv["x"], lv["delta"], lv["A"], lv["B"], lv["C"], lv["D"], z=lv["z"])
+        y.backward(inp["gy"].to(DEV))
+        torch.cuda.synchronize()
+    finally:
+        dist.destroy_process_group()
+    ref = {k: inp[k].double().requires_grad_() for k in ("x", "delta", "z", "B", "C", "A", "D")}
+    yo = O.selective_scan_f64(ref["x"], ref["delta"], ref["A"], ref["B"], ref["C"], ref["D"], z=ref["z"])
+    yo.backward(inp["gy"].double())
+    assert_close(y, yo.float(), RTOL, ATOL, "y")
+    for k in ref:
+        scale = ref[k].grad.abs().max().item()
+        assert_close(lv[k].grad, ref[k].grad.float(), RTOL, max(ATOL, ATOL * scale * 4), f"grad {k}")
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -73,7 +73,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, use_bias, out):
+def _worker(rank, world, port, use_bias, out, S=1):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -87,19 +87,19 @@ def _worker(rank, world, port, use_bias, out):
         sl = lambda t: t[:, rank * Ls:(rank + 1) * Ls].double()
         args = (sl(inp["x"]), sl(inp["delta"]), inp["A"].double(), sl(inp["B"]), sl(inp["C"]),
                 inp["D"].double(), sl(inp["z"]), None if bias is None else bias.double())
-        y, h_in, P_all, carries, hT = lshard.sharded_forward(OracleOps, dist.group.WORLD, *args)
-        grads = lshard.sharded_backward(OracleOps, dist.group.WORLD, *args, sl(inp["gy"]), carries, P_all)
+        y, h_in, P_all, carries, hT = lshard.sharded_forward(OracleOps, dist.group.WORLD, *args, subshards=S)
+        grads = lshard.sharded_backward(OracleOps, dist.group.WORLD, *args, sl(inp["gy"]), h_in, P_all, subshards=S)
         out[rank] = dict(y=y.detach(), grads=[None if t is None else t.detach() for t in grads])
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("use_bias", [False, True])
-def test_two_cpu_ranks_reproduce_the_single_sequence(use_bias):
+@pytest.mark.parametrize("use_bias,S", [(False, 1), (True, 1), (True, 3)])
+def test_two_cpu_ranks_reproduce_the_single_sequence(use_bias, S):
     world = 2
     mgr = mp.Manager()
     out = mgr.dict()
-    mp.start_processes(_worker, args=(world, _free_port(), use_bias, out), nprocs=world, join=True,
+    mp.start_processes(_worker, args=(world, _free_port(), use_bias, out, S), nprocs=world, join=True,
                        start_method="spawn")
     # single-sequence answer
     inp = scan_inputs(77, 2, 48, 6, 8, structured_A=False, big_delta=True)
@@ -125,3 +125,11 @@ def test_two_cpu_ranks_reproduce_the_single_sequence(use_bias):
             assert torch.allclose(out[r]["grads"][7], bl.grad, **tol)
     # the carry leaving rank 0 to the left is the gradient w.r.t. a (zero) initial state
     assert out[0]["grads"][8].shape == (2, 6, 8)
+
+
+def test_pick_subshards():
+    from mamba_b200.lshard import pick_subshards
+    assert pick_subshards(8, 2048, 1536, 1) == 1            # already enough rows x channel tiles
+    assert pick_subshards(1, 131072, 5120, 1) == 8          # one long row: cut it up
+    assert pick_subshards(1, 16384, 5120, 8) == 8
+    assert pick_subshards(1, 40, 5120, 1) == 1              # not divisible into 16-step pieces
