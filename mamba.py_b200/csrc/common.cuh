@@ -95,7 +95,7 @@ __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
 // Producer and consumer warps of one CTA hand tiles to each other through these.  A wait
 // that does not complete within kSpinLimit polls gives up and reports it; nothing spins
 // without a limit.
-constexpr int kSpinLimit = 1 << 20;          // polls of at most ~1 us each: gives up after about a second
+constexpr int kSpinLimit = 1 << 22;          // polls at least 100 ns apart: gives up after roughly a second
 enum { MB200_DEV_OK = 0, MB200_DEV_WAIT_TIMEOUT = 1 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -109,19 +109,25 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
                : "memory");
 }
 // true when the phase with the given parity has completed; false after kSpinLimit polls.
-// Each poll lets the hardware suspend the thread for up to 1 us while the phase is pending.
+// A pending poll is followed by a short sleep: a waiting warp must not spend issue slots and
+// shared-memory bandwidth (the poll is a shared-memory access) that the working warps need.
+__device__ __forceinline__ bool mbar_poll(uint32_t addr, int parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(addr), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity) {
   const uint32_t addr = smem_u32(bar);
+  if (mbar_poll(addr, parity)) return true;
   for (int i = 0; i < kSpinLimit; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(addr), "r"(parity), "r"(1000)
-        : "memory");
-    if (ok) return true;
+    __nanosleep(100);
+    if (mbar_poll(addr, parity)) return true;
   }
   return false;
 }

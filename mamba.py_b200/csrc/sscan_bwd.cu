@@ -173,7 +173,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
 #pragma unroll
       for (int t = 0; t < kHalf; ++t) step(t, hmid);          // state entering the second half
 
-#pragma unroll
+#pragma unroll 1
       for (int half = 1; half >= 0; --half) {
         // states after each step of this half, in registers
         float2 hh[kHalf][2];
@@ -339,10 +339,12 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
         const float* src = reinterpret_cast<const float*>(
                                s_ep + wb * kBWin * 2 * 4 * kEpStride + ((ti * 2 + which) * 4 + qq) * kEpStride) + 2 * hf;
         float2 acc0 = make_float2(0.f, 0.f), acc1 = acc0;
+        // lanes of the dC rows start one channel later than those of the dB rows: with 8 banks between
+        // consecutive rows this spreads a half-warp's 16 loads over all 32 banks
 #pragma unroll
         for (int k = 0; k < kBTE; k += 2) {
-          acc0 = __fadd2_rn(acc0, *reinterpret_cast<const float2*>(src + 4 * k));
-          acc1 = __fadd2_rn(acc1, *reinterpret_cast<const float2*>(src + 4 * (k + 1)));
+          acc0 = __fadd2_rn(acc0, *reinterpret_cast<const float2*>(src + 4 * ((k + which) & (kBTE - 1))));
+          acc1 = __fadd2_rn(acc1, *reinterpret_cast<const float2*>(src + 4 * ((k + 1 + which) & (kBTE - 1))));
         }
         mbar_arrive(&win_empty[wb]);
         const int64_t t = t0 + win_t(wl) + ti;
