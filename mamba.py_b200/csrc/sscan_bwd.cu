@@ -121,6 +121,13 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
   __syncthreads();
   auto fail = [&]() { atomicExch(&g_bwd_status, MB200_DEV_WAIT_TIMEOUT); };
 
+  // The recurrence warps need far more registers than the others: hand 32 registers per thread of
+  // warps 4-7 over to warps 0-3 (the kernel is compiled for 80; 128 * 48 + 128 * 112 = 256 * 80).
+  if (warp < 4) {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 112;");
+  } else {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
+  }
   if (warp < 4) {
     // ================================================================== consumers
     const int e_l = tid >> 2, q = tid & 3;
