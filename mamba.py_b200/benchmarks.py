@@ -95,8 +95,24 @@ def bench_decode(args, rank, world, dev, ClockSampler, time_region, time_kernel)
         for _ in range(4):
             one()
             conv_one()
-        k_ms, k_min = time_kernel(one, 32)
-        c_ms, c_min = time_kernel(conv_one, 32)
+
+        def graph_time(fn, launches):
+            """Device time per launch with the host out of the way: `launches` calls in one CUDA graph."""
+            st = torch.cuda.Stream()
+            st.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(st):
+                fn()
+            torch.cuda.current_stream().wait_stream(st)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(launches):
+                    fn()
+            g.replay()
+            ms, mn = time_kernel(g.replay, 8)
+            return ms / launches, mn / launches
+
+        k_ms, k_min = graph_time(one, n_layers)
+        c_ms, c_min = graph_time(conv_one, n_layers)
         state_bytes = 2 * Bsz * ED * N * 4 + 4 * Bsz * ED * 2 + 2 * Bsz * N * 2
         conv_bytes = 2 * Bsz * ED * (K - 1) * 2 + 2 * Bsz * ED * 2
         res["kernels"] = {

@@ -13,7 +13,7 @@ namespace {
 
 constexpr int kStepThreads = 256;
 
-template <typename T, int N>
+template <typename T, int N, bool kVecBC>
 __global__ void __launch_bounds__(kStepThreads)
 ssm_step_kernel(const T* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ z,
                 const float* __restrict__ A, const T* __restrict__ Bm, const T* __restrict__ Cm,
@@ -30,22 +30,34 @@ ssm_step_kernel(const T* __restrict__ x, const T* __restrict__ delta, const T* _
   const bool ok = e < ED;
   float yv = 0.f, xv = 0.f;
   if (ok) {
-    xv = Elem<T>::to_f(x[b * x_sb + e]);
-    float dv = Elem<T>::to_f(delta[b * d_sb + e]);
-    if (flags & MB200_DELTA_SOFTPLUS) dv = softplusf(dv + delta_bias[e]);
-    const float4 Av = *reinterpret_cast<const float4*>(A + e * N + 4 * q);
+    // the state is the only large stream: get it moving first, everything else is small
     float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
     if (h_in) hv = __ldcs(reinterpret_cast<const float4*>(h_in + (b * ED + e) * N + 4 * q));
+    const float4 Av = *reinterpret_cast<const float4*>(A + e * N + 4 * q);
+    float b4[4], c4[4];
+    if constexpr (kVecBC) {
+      const Vec4<T> bv = *reinterpret_cast<const Vec4<T>*>(Bm + b * b_sb + 4 * q);
+      const Vec4<T> cv = *reinterpret_cast<const Vec4<T>*>(Cm + b * c_sb + 4 * q);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { b4[j] = Elem<T>::to_f(bv.v[j]); c4[j] = Elem<T>::to_f(cv.v[j]); }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        b4[j] = Elem<T>::to_f(Bm[b * b_sb + 4 * q + j]);
+        c4[j] = Elem<T>::to_f(Cm[b * c_sb + 4 * q + j]);
+      }
+    }
+    xv = Elem<T>::to_f(x[b * x_sb + e]);
+    float dv = Elem<T>::to_f(delta[b * d_sb + e]);
+    if (flags & MB200_DELTA_SOFTPLUS) dv = softplus_fast(dv + delta_bias[e]);
     const float a4[4] = {Av.x, Av.y, Av.z, Av.w};
     float h4[4] = {hv.x, hv.y, hv.z, hv.w};
-    const float dx = dv * xv;
+    const float dx = dv * xv, d2 = dv * kLog2e;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const float a = ex2f(dv * a4[j] * kLog2e);
-      const float bj = Elem<T>::to_f(Bm[b * b_sb + 4 * q + j]);
-      const float cj = Elem<T>::to_f(Cm[b * c_sb + 4 * q + j]);
-      h4[j] = fmaf(a, h4[j], dx * bj);
-      yv = fmaf(h4[j], cj, yv);
+      const float a = ex2f(d2 * a4[j]);
+      h4[j] = fmaf(a, h4[j], dx * b4[j]);
+      yv = fmaf(h4[j], c4[j], yv);
     }
     __stcs(reinterpret_cast<float4*>(h_out + (b * ED + e) * N + 4 * q),
            make_float4(h4[0], h4[1], h4[2], h4[3]));
@@ -56,7 +68,7 @@ ssm_step_kernel(const T* __restrict__ x, const T* __restrict__ delta, const T* _
     yv = fmaf(D ? D[e] : 0.f, xv, yv);
     if (z) {
       const float zv = Elem<T>::to_f(z[b * z_sb + e]);
-      yv *= zv * sigmoidf(zv);
+      yv *= zv * sigmoid_fast(zv);
     }
     y[b * y_sb + e] = Elem<T>::from_f(yv);
   }
@@ -81,6 +93,44 @@ __global__ void conv_step_kernel(const T* __restrict__ xin, const T* __restrict_
   for (int k = 0; k < K; ++k) acc = fmaf(w[e * K + k], win[k], acc);
   for (int k = 0; k < K - 1; ++k) co[k] = Elem<T>::from_f(win[k + 1]);
   xc[b * ED + e] = Elem<T>::from_f(acc * sigmoidf(acc));
+}
+
+// Same for the common d_conv = 4: a thread owns 4 neighbouring channels, so the 3-wide windows of
+// those channels (12 contiguous elements) and the new inputs move as 8- or 16-byte vectors.
+template <typename T>
+__global__ void __launch_bounds__(256)
+conv_step_k4_kernel(const T* __restrict__ xin, const T* __restrict__ conv_in, const float* __restrict__ w,
+                    const float* __restrict__ bias, T* __restrict__ xc, T* __restrict__ conv_out,
+                    int64_t ED, int64_t x_sb) {
+  const int64_t e = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) * 4;
+  const int64_t b = blockIdx.y;
+  if (e >= ED) return;
+  const Vec4<T>* ci = reinterpret_cast<const Vec4<T>*>(conv_in + (b * ED + e) * 3);
+  Vec4<T>* co = reinterpret_cast<Vec4<T>*>(conv_out + (b * ED + e) * 3);
+  const Vec4<T> w0 = ci[0], w1 = ci[1], w2 = ci[2];            // 12 window values of 4 channels
+  const Vec4<T> xn = *reinterpret_cast<const Vec4<T>*>(xin + b * x_sb + e);
+  T win[12] = {w0.v[0], w0.v[1], w0.v[2], w0.v[3], w1.v[0], w1.v[1], w1.v[2], w1.v[3],
+               w2.v[0], w2.v[1], w2.v[2], w2.v[3]};
+  T out[12];
+  Vec4<T> xo;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const float4 wf = *reinterpret_cast<const float4*>(w + (e + c) * 4);
+    float acc = bias ? bias[e + c] : 0.f;
+    acc = fmaf(wf.x, Elem<T>::to_f(win[3 * c]), acc);
+    acc = fmaf(wf.y, Elem<T>::to_f(win[3 * c + 1]), acc);
+    acc = fmaf(wf.z, Elem<T>::to_f(win[3 * c + 2]), acc);
+    acc = fmaf(wf.w, Elem<T>::to_f(xn.v[c]), acc);
+    out[3 * c] = win[3 * c + 1];
+    out[3 * c + 1] = win[3 * c + 2];
+    out[3 * c + 2] = xn.v[c];
+    xo.v[c] = Elem<T>::from_f(acc * sigmoid_fast(acc));
+  }
+  Vec4<T> o0, o1, o2;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { o0.v[k] = out[k]; o1.v[k] = out[4 + k]; o2.v[k] = out[8 + k]; }
+  co[0] = o0; co[1] = o1; co[2] = o2;
+  *reinterpret_cast<Vec4<T>*>(xc + b * ED + e) = xo;
 }
 
 // Fold of all-gathered shard carries (see mamba_b200.h).
@@ -141,13 +191,20 @@ static int ssm_step_t(const void* x, const void* delta, const void* z, const flo
                       const float* h_in, float* h_out, void* y, int64_t B, int64_t ED, int N,
                       int64_t x_sb, int64_t d_sb, int64_t z_sb, int64_t b_sb, int64_t c_sb,
                       int64_t y_sb, int flags, cudaStream_t st) {
+  const bool vec_bc = (reinterpret_cast<uintptr_t>(Bm) % (4 * sizeof(T)) == 0) &&
+                      (reinterpret_cast<uintptr_t>(Cm) % (4 * sizeof(T)) == 0) && b_sb % 4 == 0 && c_sb % 4 == 0;
 #define MB200_STEP(NN)                                                                          \
   {                                                                                             \
     constexpr int epb = kStepThreads / (NN / 4);                                                \
     dim3 grid(unsigned((ED + epb - 1) / epb), unsigned(B));                                     \
-    ssm_step_kernel<T, NN><<<grid, kStepThreads, 0, st>>>(                                      \
-        (const T*)x, (const T*)delta, (const T*)z, A, (const T*)Bm, (const T*)Cm, D, delta_bias, \
-        h_in, h_out, (T*)y, ED, x_sb, d_sb, z_sb, b_sb, c_sb, y_sb, flags);                     \
+    if (vec_bc)                                                                                 \
+      ssm_step_kernel<T, NN, true><<<grid, kStepThreads, 0, st>>>(                              \
+          (const T*)x, (const T*)delta, (const T*)z, A, (const T*)Bm, (const T*)Cm, D, delta_bias, \
+          h_in, h_out, (T*)y, ED, x_sb, d_sb, z_sb, b_sb, c_sb, y_sb, flags);                   \
+    else                                                                                        \
+      ssm_step_kernel<T, NN, false><<<grid, kStepThreads, 0, st>>>(                             \
+          (const T*)x, (const T*)delta, (const T*)z, A, (const T*)Bm, (const T*)Cm, D, delta_bias, \
+          h_in, h_out, (T*)y, ED, x_sb, d_sb, z_sb, b_sb, c_sb, y_sb, flags);                   \
     return check_launch();                                                                      \
   }
   switch (N) {
@@ -192,6 +249,19 @@ extern "C" int mb200_conv_step(const void* xin, const void* conv_in, const float
   if (!xin || !w || !xc || (K > 1 && (!conv_in || !conv_out))) return MB200_EINVAL;
   if (B > 65535) return MB200_ETOOBIG;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int es = dtype == MB200_F32 ? 4 : 2;
+  if (K == 4 && ED % 4 == 0 && aligned16(xin) && aligned16(conv_in) && aligned16(conv_out) && aligned16(xc) &&
+      aligned16(w) && (x_sb * es) % 16 == 0) {
+    dim3 g4(unsigned((ED / 4 + 255) / 256), unsigned(B));
+    if (dtype == MB200_F32)
+      conv_step_k4_kernel<float><<<g4, 256, 0, st>>>((const float*)xin, (const float*)conv_in, w, bias,
+                                                     (float*)xc, (float*)conv_out, ED, x_sb);
+    else
+      conv_step_k4_kernel<__nv_bfloat16><<<g4, 256, 0, st>>>(
+          (const __nv_bfloat16*)xin, (const __nv_bfloat16*)conv_in, w, bias, (__nv_bfloat16*)xc,
+          (__nv_bfloat16*)conv_out, ED, x_sb);
+    return check_launch();
+  }
   dim3 grid(unsigned((ED + 255) / 256), unsigned(B));
   if (dtype == MB200_F32)
     conv_step_kernel<float><<<grid, 256, 0, st>>>((const float*)xin, (const float*)conv_in, w, bias,
