@@ -196,6 +196,25 @@ int mb200_conv_step(const void* xin, const void* conv_in, const float* w, const 
                     void* xc, void* conv_out,
                     int64_t B, int64_t ED, int K, int64_t x_sb, int dtype, void* stream);
 
+/* ---- Depthwise causal conv1d + SiLU in the (B, L, ED) layout, d_conv = 4 (K must be 4, else
+ * MB200_ETOOBIG).  Replaces the transpose / nn.Conv1d(padding=3) / slice / transpose / F.silu sequence
+ * of MambaBlock.forward (mambapy/mamba.py:217-221):
+ *   y[b,t,e] = silu( bias[e] + sum_k w[e,k] * x[b, t-3+k, e] ),  x[b, t<0, e] = 0.
+ * x, y: (B, L, ED) activations with strides (sb, sl); w: (ED, 4) float32 dense; bias: (ED) or NULL. */
+int mb200_conv1d_silu_fwd(const void* x, const float* w, const float* bias, void* y,
+                          int64_t B, int64_t L, int64_t ED, int K,
+                          int64_t x_sb, int64_t x_sl, int64_t y_sb, int64_t y_sl,
+                          int dtype, void* stream);
+
+/* Backward of mb200_conv1d_silu_fwd (what autograd derives for mambapy/mamba.py:217-221).
+ * dy in; dx out (activation dtype); dw (ED, 4) and dbias (ED, may be NULL) float32, ACCUMULATED into
+ * (caller zero-fills).  The pre-activation is recomputed from x. */
+int mb200_conv1d_silu_bwd(const void* x, const float* w, const float* bias, const void* dy,
+                          void* dx, float* dw, float* dbias,
+                          int64_t B, int64_t L, int64_t ED, int K,
+                          int64_t x_sb, int64_t x_sl, int64_t dy_sb, int64_t dy_sl,
+                          int64_t dx_sb, int64_t dx_sl, int dtype, void* stream);
+
 /* ---- Sequence-sharded scan: fold the per-shard carries after they were all-gathered.
  * No reference counterpart (the reference is single-device); the single-device answer on
  * the concatenated sequence is what it must reproduce.

@@ -198,7 +198,7 @@ class LShardSelectiveScanFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, delta, A, Bm, Cm, D, z, delta_bias, group):
         _require_cuda(x, delta, A, Bm, Cm, D, z, delta_bias)
-        dt = _act_dtype(x)
+        dt = _act_dtype(x, delta, z, Bm, Cm)
         xs, ds, zs = _rows(x, dt), _rows(delta, dt), _rows(z, dt)
         Bs, Cs = _rows(Bm, dt), _rows(Cm, dt)
         A32, D32, b32 = _f32(A), _f32(D), _f32(delta_bias)

@@ -39,10 +39,15 @@ def _rows(t: torch.Tensor | None, dtype) -> torch.Tensor | None:
     return t
 
 
-def _act_dtype(x: torch.Tensor):
-    if x.dtype in (torch.float32, torch.bfloat16):
-        return x.dtype
-    raise TypeError(f"mamba_b200 kernels take float32 or bfloat16 activations, got {x.dtype}")
+def _act_dtype(x: torch.Tensor, *others):
+    """Activation dtype the kernel runs in: bfloat16 only when EVERY activation tensor is bfloat16,
+    float32 as soon as one of them is (under autocast the reference keeps delta in float32 while x, B
+    and C are bfloat16, mambapy/mamba.py:264-265; rounding delta to bfloat16 would change the decay)."""
+    dts = {t.dtype for t in (x,) + others if t is not None}
+    for d in dts:
+        if d not in (torch.float32, torch.bfloat16):
+            raise TypeError(f"mamba_b200 kernels take float32 or bfloat16 activations, got {d}")
+    return torch.bfloat16 if dts == {torch.bfloat16} else torch.float32
 
 
 def _f32(t):
@@ -116,7 +121,7 @@ class SelectiveScanFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, delta, A, Bm, Cm, D, z, delta_bias, h0, return_last_state):
         _require_cuda(x, delta, A, Bm, Cm, D, z, delta_bias, h0)
-        dt = _act_dtype(x)
+        dt = _act_dtype(x, delta, z, Bm, Cm)
         xs, ds, zs = _rows(x, dt), _rows(delta, dt), _rows(z, dt)
         Bs, Cs = _rows(Bm, dt), _rows(Cm, dt)
         A32, D32, b32, h032 = _f32(A), _f32(D), _f32(delta_bias), _f32(h0)
@@ -178,7 +183,7 @@ def ssm_step_fn(x, h, delta, A, B, C, D=None, z=None, delta_bias=None, inplace=F
     overwrites a float32 contiguous `h` instead and returns it."""
     _require_cuda(x, delta, A, B, C, D, z, delta_bias, h)
     lib = _lib.load()
-    dt = _act_dtype(x)
+    dt = _act_dtype(x, delta, z, B, C)
     xs, ds, zs, Bs, Cs = (_rows(t, dt) for t in (x, delta, z, B, C))
     A32, D32, b32 = _f32(A), _f32(D), _f32(delta_bias)
     h32 = None if h is None else h.float().contiguous()
@@ -233,6 +238,56 @@ def conv_step_fn(x, inputs, weight, bias, inplace=False):
     return xc, new_win
 
 
+class CausalConv1dSiluFn(torch.autograd.Function):
+    """silu(depthwise causal conv1d(x)) on (B, L, ED) tensors, d_conv = 4."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        _require_cuda(x, weight, bias)
+        lib = _lib.load()
+        dt = _act_dtype(x)
+        xs = _rows(x, dt)
+        Bsz, L, ED = xs.shape
+        K = weight.shape[-1]
+        w32 = weight.detach().reshape(ED, K).float().contiguous()
+        b32 = _f32(bias)
+        y = torch.empty((Bsz, L, ED), dtype=dt, device=xs.device)
+        with torch.cuda.device(xs.device):
+            rc = lib.mb200_conv1d_silu_fwd(xs.data_ptr(), w32.data_ptr(), _lib.ptr(b32), y.data_ptr(), Bsz, L, ED, K,
+                                           xs.stride(0), xs.stride(1), y.stride(0), y.stride(1),
+                                           _lib.dtype_code(dt), _lib.current_stream(xs.device))
+        _lib.check(rc, "mb200_conv1d_silu_fwd")
+        ctx.save_for_backward(xs, w32, b32)
+        ctx.meta = (x.dtype, weight.dtype, weight.shape, None if bias is None else bias.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xs, w32, b32 = ctx.saved_tensors
+        lib = _lib.load()
+        dy = _rows(dy, xs.dtype)
+        Bsz, L, ED = xs.shape
+        K = w32.shape[1]
+        dx = torch.empty_like(xs)
+        dw = torch.zeros_like(w32)
+        db = torch.zeros(ED, dtype=torch.float32, device=xs.device) if b32 is not None else None
+        with torch.cuda.device(xs.device):
+            rc = lib.mb200_conv1d_silu_bwd(xs.data_ptr(), w32.data_ptr(), _lib.ptr(b32), dy.data_ptr(), dx.data_ptr(),
+                                           dw.data_ptr(), _lib.ptr(db), Bsz, L, ED, K, xs.stride(0), xs.stride(1),
+                                           dy.stride(0), dy.stride(1), dx.stride(0), dx.stride(1),
+                                           _lib.dtype_code(xs.dtype), _lib.current_stream(xs.device))
+        _lib.check(rc, "mb200_conv1d_silu_bwd")
+        tx, tw, wshape, tb = ctx.meta
+        return dx.to(tx), dw.to(tw).reshape(wshape), None if db is None else db.to(tb)
+
+
+def causal_conv1d_silu(x, weight, bias=None):
+    """silu(conv1d(x)) of MambaBlock.forward (mambapy/mamba.py:217-221) without the transposes.
+
+    x: (B, L, ED); weight: (ED, 1, 4) as nn.Conv1d(groups=ED) holds it; bias: (ED) or None."""
+    return CausalConv1dSiluFn.apply(x, weight, bias)
+
+
 def _project(self, x):
     """delta (pre-softplus, without bias), B, C from x as in mambapy/mamba.py:393-396."""
     cfg = self.config
@@ -281,7 +336,9 @@ def forward(self, x):
     _, L, _ = x.shape
     xz = self.in_proj(x)
     xs, z = xz.chunk(2, dim=-1)
-    xs = self.conv1d(xs.transpose(1, 2))[:, :, :L].transpose(1, 2)
-    xs = F.silu(xs)
+    if self.conv1d.weight.shape[-1] == 4:
+        xs = causal_conv1d_silu(xs, self.conv1d.weight, self.conv1d.bias)
+    else:
+        xs = F.silu(self.conv1d(xs.transpose(1, 2))[:, :, :L].transpose(1, 2))
     y = ssm(self, xs, z)
     return self.out_proj(y)

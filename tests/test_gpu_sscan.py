@@ -187,6 +187,20 @@ def test_linearity_in_x_full_width():
     assert torch.allclose(y2, 2 * y1, rtol=1e-6, atol=1e-6)
 
 
+def test_mixed_dtypes_run_in_float32():
+    """bf16 x, B, C with a float32 delta (what autocast gives the reference): nothing is rounded to
+    bf16 behind the caller's back; the kernel runs in float32 and returns float32 like the reference."""
+    import mamba_b200
+    inp = scan_inputs(21, 2, 40, 32, 16, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(3)
+    inp["delta"] = torch.nn.functional.softplus(torch.randn(2, 40, 32, generator=g) * 0.5 - 3.0)   # full float32
+    y = mamba_b200.selective_scan_fn(inp["x"].to(DEV).bfloat16(), inp["delta"].to(DEV), inp["A"].to(DEV),
+                                     inp["B"].to(DEV).bfloat16(), inp["C"].to(DEV).bfloat16(), inp["D"].to(DEV))
+    assert y.dtype == torch.float32
+    yo = O.selective_scan_f64(inp["x"], inp["delta"], inp["A"], inp["B"], inp["C"], inp["D"])
+    assert_close(y, yo.float(), RTOL, ATOL)
+
+
 def test_empty_and_errors():
     import mamba_b200
     z = lambda *s: torch.zeros(*s, device=DEV)
