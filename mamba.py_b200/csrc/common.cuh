@@ -108,6 +108,13 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar))
                : "memory");
 }
+// Arrival that only says "I have finished READING what this barrier guards" (the values read have
+// already been consumed by earlier instructions).  It orders nothing, so it does not wait for the
+// thread's outstanding global stores or reductions the way a releasing arrive does.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint64_t* bar) {
+  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.relaxed.cta.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar))
+               : "memory");
+}
 // true when the phase with the given parity has completed; false after kSpinLimit polls.
 // A pending poll is followed by a short sleep: a waiting warp must not spend issue slots and
 // shared-memory bandwidth (the poll is a shared-memory access) that the working warps need.
@@ -119,6 +126,20 @@ __device__ __forceinline__ bool mbar_poll(uint32_t addr, int parity) {
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(addr), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Non-blocking test of a phase.  Issued ahead of the work that does not need the answer, it takes
+// the barrier's round trip through the shared-memory pipe off the critical path; mbar_wait follows
+// only when the answer was "not yet".
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, int parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
   return ok != 0;
 }

@@ -5,9 +5,10 @@
 
 namespace mb200 {
 
-// Timesteps between two saved states.  The backward kernel keeps one chunk of decay factors
-// and states in registers (2 * kChunk * 4 floats per thread), which fixes this at 16.
-constexpr int kChunk = 16;
+// Timesteps between two saved states.  The backward kernels keep the states of one chunk in
+// registers while they walk it in reverse (kChunk * 4 floats per thread), which fixes this at 8:
+// the saved states cost kChunk times less memory than the full state tensor the reference keeps.
+constexpr int kChunk = 8;
 
 // A thread owns 4 states of one channel, so N/4 lanes share a channel and a 128-thread CTA
 // covers 128/(N/4) channels.  kTT is the number of timesteps staged per shared-memory tile.

@@ -28,8 +28,8 @@ namespace {
 
 constexpr int kBN = 16;                      // d_state of this path
 constexpr int kBTE = 32;                     // channels per CTA
-constexpr int kBTile = kChunk;               // timesteps per tile
-constexpr int kHalf = kBTile / 2;            // states kept in registers at a time
+constexpr int kBTile = 2 * kChunk;           // timesteps per tile (two saved states per tile)
+constexpr int kHalf = kChunk;                // states kept in registers at a time
 constexpr int kBWin = 2;                     // timesteps per reduction window
 constexpr int kWinsPerTile = kBTile / kBWin;
 constexpr int kBwdThreads = 256;
@@ -55,17 +55,19 @@ template <typename T> struct TmaBwdSmem {
   static constexpr int kDyp = kOp + 2 * kBTile * kBTE * 8;                // float  [2][16][32]
   static constexpr int kB = kDyp + 2 * kBTile * kBTE * 4;                 // float  [2][16][16]
   static constexpr int kC = kB + 2 * kBTile * kBN * 4;
-  static constexpr int kNp = kC + 2 * kBTile * kBN * 4;                   // float4 [2][kBWin][128]
-  static constexpr int kEp = kNp + 2 * kBWin * 128 * 16;                  // float4 [2][kBWin][2][4][kEpStride]
+  static constexpr int kNp = kC + 2 * kBTile * kBN * 4;                   // float  [2][kBWin][3][128]
+  static constexpr int kEp = kNp + 2 * kBWin * 3 * 128 * 4;                  // float4 [2][kBWin][2][4][kEpStride]
   static constexpr int kD = kEp + 2 * kBWin * 2 * 4 * kEpStride * 16;     // float [32]
   static constexpr int kBias = kD + kBTE * 4;
   static constexpr int kBars = kBias + kBTE * 4;                          // 2*kStages + 8 mbarriers
   static constexpr int kBytes = kBars + (2 * kStages + 8) * 8;
 };
 
-// float4 slot of consumer thread `tid` in a row of the n-partials tile (XOR keeps the finishing
-// warps' reads mostly conflict free; writes stay a permutation inside each warp)
-__device__ __forceinline__ int np_slot(int tid) { return tid ^ ((tid >> 3) & 7); }
+// The partial sums over a thread's 4 states (for y, dx, ddelta) go to three planes of 128 floats per
+// timestep; the 4 lanes of a channel are neighbours, so a finishing thread fetches one sum of one
+// channel with a single 16-byte load.  np_chan(c) is the float4 position of channel c in a plane: the
+// XOR keeps the finishing warps' loads (channels 2l, 2l+1 per lane) free of bank conflicts.
+__device__ __forceinline__ int np_chan(int c) { return c ^ ((c >> 3) & 1); }
 
 __device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
   asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
@@ -83,7 +85,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
   float* s_dyp = reinterpret_cast<float*>(smem_raw + S::kDyp);
   float* s_B = reinterpret_cast<float*>(smem_raw + S::kB);
   float* s_C = reinterpret_cast<float*>(smem_raw + S::kC);
-  float4* s_np = reinterpret_cast<float4*>(smem_raw + S::kNp);
+  float* s_np = reinterpret_cast<float*>(smem_raw + S::kNp);
   float4* s_ep = reinterpret_cast<float4*>(smem_raw + S::kEp);
   float* s_D = reinterpret_cast<float*>(smem_raw + S::kD);
   float* s_bias = reinterpret_cast<float*>(smem_raw + S::kBias);
@@ -108,7 +110,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
     for (int i = 0; i < kStages; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_free[i], 96); }
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&op_full[i], 32); mbar_init(&op_empty[i], 128);
+      mbar_init(&op_full[i], 32); mbar_init(&op_empty[i], 128 + 64);
       mbar_init(&win_full[i], 128); mbar_init(&win_empty[i], 64);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -146,18 +148,20 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
       dAacc[0] = dAacc[1] = make_float2(0.f, 0.f);
     }
     const int op_off0 = op_index(0, e_l, kBTE), op_off1 = op_index(1, e_l, kBTE) - kBTE;
-    const int npo = np_slot(tid);
-    const float* carry_base = p.carries + (b * ntiles * p.ED + e) * N + 4 * q;
-    auto load_carry = [&](int64_t kt) {
-      return e_ok ? *reinterpret_cast<const float4*>(carry_base + kt * p.ED * N) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const int npo = np_chan(e_l) * 4 + q;
+    const int64_t nchunks = (p.L + kHalf - 1) / kHalf;
+    const float* carry_base = p.carries + (b * nchunks * p.ED + e) * N + 4 * q;
+    auto load_carry = [&](int64_t c) {
+      return (e_ok && c < nchunks) ? *reinterpret_cast<const float4*>(carry_base + c * p.ED * N)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
     };
-    float4 carry_next = load_carry(ntiles - 1);
+    float4 carry_next = load_carry(2 * (ntiles - 1)), carry_next_mid = load_carry(2 * (ntiles - 1) + 1);
 
     for (int64_t j = 0; j < ntiles; ++j) {
       const int64_t kt = ntiles - 1 - j;
       const int buf = int(j & 1);
-      const float4 cv = carry_next;
-      if (kt > 0) carry_next = load_carry(kt - 1);
+      const float4 cv = carry_next, cm = carry_next_mid;
+      if (kt > 0) { carry_next = load_carry(2 * kt - 2); carry_next_mid = load_carry(2 * kt - 1); }
       if (!mbar_wait(&op_full[buf], int((j >> 1) & 1))) { fail(); return; }
       const float2* op = s_op + buf * kBTile * kBTE;
       const float* dyp = s_dyp + buf * kBTile * kBTE + e_l;
@@ -166,7 +170,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
       const float2 hp[2] = {make_float2(cv.x, cv.y), make_float2(cv.z, cv.w)};   // state entering the tile
 
       // one forward step of the recurrence from operands in shared memory
-      auto step = [&](int t, float2 (&h)[2]) {
+      auto step = [&](int t, float2 (&h)[2], float2 (&av)[2]) {
         const float2 o = op[t * kBTE + ((t & 1) ? op_off1 : op_off0)];
         const float4 Bq = *reinterpret_cast<const float4*>(sB + t * N);
         const float2 dd = make_float2(o.x, o.x), dxx = make_float2(o.y, o.y);
@@ -174,11 +178,9 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
         const float2 a0 = make_float2(ex2f(e0v.x), ex2f(e0v.y)), a1 = make_float2(ex2f(e1v.x), ex2f(e1v.y));
         h[0] = __ffma2_rn(a0, h[0], __fmul2_rn(dxx, make_float2(Bq.x, Bq.y)));
         h[1] = __ffma2_rn(a1, h[1], __fmul2_rn(dxx, make_float2(Bq.z, Bq.w)));
+        av[0] = a0; av[1] = a1;
       };
-
-      float2 hmid[2] = {hp[0], hp[1]};
-#pragma unroll
-      for (int t = 0; t < kHalf; ++t) step(t, hmid);          // state entering the second half
+      const float2 hmid[2] = {make_float2(cm.x, cm.y), make_float2(cm.z, cm.w)};   // state entering the second half
 
 #pragma unroll 1
       for (int half = 1; half >= 0; --half) {
@@ -188,26 +190,42 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
           float2 h[2] = {half ? hmid[0] : hp[0], half ? hmid[1] : hp[1]};
 #pragma unroll
           for (int i = 0; i < kHalf; ++i) {
-            step(half * kHalf + i, h);
+            float2 adrop[2];
+            step(half * kHalf + i, h, adrop);
             hh[i][0] = h[0]; hh[i][1] = h[1];
           }
         }
+        // operands of the reverse walk are fetched one timestep ahead, so that their trip through the
+        // shared-memory pipe overlaps the previous timestep's arithmetic, stores and barrier traffic
+        struct Opnd { float2 o; float dy; float4 B, C; };
+        auto fetch = [&](int t) {
+          Opnd r;
+          r.o = op[t * kBTE + ((t & 1) ? op_off1 : op_off0)];
+          r.dy = dyp[t * kBTE];
+          r.B = *reinterpret_cast<const float4*>(sB + t * N);
+          r.C = *reinterpret_cast<const float4*>(sC + t * N);
+          return r;
+        };
+        Opnd nx = fetch(half * kHalf + kHalf - 1), nx2 = fetch(half * kHalf + kHalf - 2);
 #pragma unroll
         for (int wi = kHalf / kBWin - 1; wi >= 0; --wi) {
           // window sequence number: tiles in processing order, windows from the tile's end
           const int64_t wseq = j * kWinsPerTile + (1 - half) * (kHalf / kBWin) + (kHalf / kBWin - 1 - wi);
           const int wb = int(wseq & 1);
-          if (wseq >= 2 && !mbar_wait(&win_empty[wb], int(((wseq - 2) >> 1) & 1))) { fail(); return; }
-          float4* np = s_np + wb * kBWin * 128;
+          // asked now, needed only before the first store of the window
+          const bool slot_free = wseq < 2 || mbar_test(&win_empty[wb], int(((wseq - 2) >> 1) & 1));
+          float* np = s_np + wb * kBWin * 3 * 128;
           float4* ep = s_ep + wb * kBWin * 2 * 4 * kEpStride;
 #pragma unroll
           for (int ti = kBWin - 1; ti >= 0; --ti) {
             const int i = wi * kBWin + ti;                    // index inside the half
             const int t = half * kHalf + i;                   // index inside the tile
-            const float2 o = op[t * kBTE + ((t & 1) ? op_off1 : op_off0)];
-            const float dyv = dyp[t * kBTE];
-            const float4 Bq = *reinterpret_cast<const float4*>(sB + t * N);
-            const float4 Cq = *reinterpret_cast<const float4*>(sC + t * N);
+            const Opnd cu = nx;
+            nx = nx2;
+            if (i > 1) nx2 = fetch(t - 2);
+            const float2 o = cu.o;
+            const float dyv = cu.dy;
+            const float4 Bq = cu.B, Cq = cu.C;
             const float2 dd = make_float2(o.x, o.x), dxx = make_float2(o.y, o.y), dy2 = make_float2(dyv, dyv);
             const float2 Bv[2] = {make_float2(Bq.x, Bq.y), make_float2(Bq.z, Bq.w)};
             const float2 Cv[2] = {make_float2(Cq.x, Cq.y), make_float2(Cq.z, Cq.w)};
@@ -215,8 +233,6 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
             float2 dBp[2], dCp[2];
 #pragma unroll
             for (int k = 0; k < 2; ++k) {
-              const float2 ev = __fmul2_rn(dd, A2[k]);
-              const float2 a = make_float2(ex2f(ev.x), ex2f(ev.y));
               const float2 hcur = hh[i][k];
               const float2 hprev = i ? hh[i - 1][k] : (half ? hmid[k] : hp[k]);
               const float2 g = __ffma2_rn(dy2, Cv[k], gc[k]);
@@ -224,12 +240,16 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
               dCp[k] = __fmul2_rn(dy2, hcur);
               dBp[k] = __fmul2_rn(g, dxx);
               gBs = __ffma2_rn(g, Bv[k], gBs);
-              const float2 w = __fmul2_rn(__fmul2_rn(g, hprev), a);
+              const float2 ev = __fmul2_rn(dd, A2[k]);
+              gc[k] = __fmul2_rn(make_float2(ex2f(ev.x), ex2f(ev.y)), g);
+              const float2 w = __fmul2_rn(gc[k], hprev);
               dAacc[k] = __ffma2_rn(w, dd, dAacc[k]);
               wAs = __ffma2_rn(w, A2[k], wAs);
-              gc[k] = __fmul2_rn(a, g);
             }
-            np[ti * 128 + npo] = make_float4(ysum.x + ysum.y, gBs.x + gBs.y, wAs.x + wAs.y, 0.f);
+            if (ti == kBWin - 1 && !slot_free && !mbar_wait(&win_empty[wb], int(((wseq - 2) >> 1) & 1))) { fail(); return; }
+            np[(ti * 3 + 0) * 128 + npo] = ysum.x + ysum.y;
+            np[(ti * 3 + 1) * 128 + npo] = gBs.x + gBs.y;
+            np[(ti * 3 + 2) * 128 + npo] = wAs.x + wAs.y;
             ep[((ti * 2 + 0) * 4 + q) * kEpStride + e_l] = make_float4(dBp[0].x, dBp[0].y, dBp[1].x, dBp[1].y);
             ep[((ti * 2 + 1) * 4 + q) * kEpStride + e_l] = make_float4(dCp[0].x, dCp[0].y, dCp[1].x, dCp[1].y);
           }
@@ -353,7 +373,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
           acc0 = __fadd2_rn(acc0, *reinterpret_cast<const float2*>(src + 4 * ((k + which) & (kBTE - 1))));
           acc1 = __fadd2_rn(acc1, *reinterpret_cast<const float2*>(src + 4 * ((k + 1 + which) & (kBTE - 1))));
         }
-        mbar_arrive(&win_empty[wb]);
+        mbar_arrive_relaxed(&win_empty[wb]);
         const int64_t t = t0 + win_t(wl) + ti;
         if (t < p.L) red_add_v2(gbase + t * N, acc0.x + acc1.x, acc0.y + acc1.y);
       }
@@ -369,37 +389,41 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
     T* odd = static_cast<T*>(p.ddelta) + b * p.dd_sb + e0 + c0;
     T* odz = has_z ? static_cast<T*>(p.dz) + b * p.dz_sb + e0 + c0 : nullptr;
     const float Dv[2] = {s_D[c0], s_D[c0 + 1]};
-    const float bv[2] = {s_bias[c0], s_bias[c0 + 1]};
     float dDacc[2] = {0.f, 0.f}, dbacc[2] = {0.f, 0.f};
     for (int64_t j = 0; j < ntiles; ++j) {
       const int64_t t0 = (ntiles - 1 - j) * kBTile;
       if (!mbar_wait(&raw_full[j % kStages], int((j / kStages) & 1))) { fail(); return; }
       const unsigned char* st = stage_ptr(j);
       const T* rx = reinterpret_cast<const T*>(st);
-      const T* rd = reinterpret_cast<const T*>(st + S::kActBytes);
       const T* rz = reinterpret_cast<const T*>(st + 2 * S::kActBytes);
       const T* rdy = reinterpret_cast<const T*>(st + 3 * S::kActBytes);
+      // delta and dy' come from the operand tile the consumers are reading (still held: this warp
+      // is one of the arrivals the converter waits for before it reuses the buffer)
+      const int buf = int(j & 1);
+      const float2* opt = s_op + buf * kBTile * kBTE;
+      const float* dyt = s_dyp + buf * kBTile * kBTE;
 #pragma unroll 1
       for (int wl = par; wl < kWinsPerTile; wl += 2) {
         const int64_t wseq = j * kWinsPerTile + wl;
         if (!mbar_wait(&win_full[par], int((wseq >> 1) & 1))) { fail(); return; }
-        const float4* np = s_np + par * kBWin * 128 + ti * 128;
+        const float4* np = reinterpret_cast<const float4*>(s_np + (par * kBWin + ti) * 3 * 128);
         float ys[2], gBs[2], wAs[2];
 #pragma unroll
         for (int k = 0; k < 2; ++k) {
-          ys[k] = gBs[k] = wAs[k] = 0.f;
-#pragma unroll
-          for (int qi = 0; qi < 4; ++qi) {
-            const float4 v = np[np_slot((c0 + k) * 4 + qi)];
-            ys[k] += v.x; gBs[k] += v.y; wAs[k] += v.z;
-          }
+          const int cs = np_chan(c0 + k);
+          const float4 v0 = np[cs], v1 = np[32 + cs], v2 = np[64 + cs];
+          ys[k] = (v0.x + v0.y) + (v0.z + v0.w);
+          gBs[k] = (v1.x + v1.y) + (v1.z + v1.w);
+          wAs[k] = (v2.x + v2.y) + (v2.z + v2.w);
         }
-        mbar_arrive(&win_empty[par]);
+        mbar_arrive_relaxed(&win_empty[par]);
         const int tt = win_t(wl) + ti;                   // timestep inside the tile
         const int64_t t = t0 + tt;
         if (t < p.L && c0 < cols_ok) {
           const Vec2<T> xv = *reinterpret_cast<const Vec2<T>*>(rx + tt * kBTE + c0);
-          const Vec2<T> dv2 = *reinterpret_cast<const Vec2<T>*>(rd + tt * kBTE + c0);
+          const float4 o4 = *reinterpret_cast<const float4*>(opt + op_index(tt, c0, kBTE));   // {delta, delta*x} x 2
+          const float2 dyg2 = *reinterpret_cast<const float2*>(dyt + tt * kBTE + c0);
+          const float dvs[2] = {o4.x, o4.z}, dygs[2] = {dyg2.x, dyg2.y};
           const Vec2<T> yv2 = *reinterpret_cast<const Vec2<T>*>(rdy + tt * kBTE + c0);
           Vec2<T> zv2 = yv2;
           if (has_z) zv2 = *reinterpret_cast<const Vec2<T>*>(rz + tt * kBTE + c0);
@@ -407,17 +431,14 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
 #pragma unroll
           for (int k = 0; k < 2; ++k) {
             const float xf = Elem<T>::to_f(xv.v[k]), dyf = Elem<T>::to_f(yv2.v[k]);
-            float dv = Elem<T>::to_f(dv2.v[k]), spg = 1.f;
-            if (softplus) {
-              const float raw = dv + bv[k];
-              dv = softplus_fast(raw);
-              spg = sigmoid_fast(raw);
-            }
-            float dyg = dyf, dzv = 0.f;
+            const float dv = dvs[k], dyg = dygs[k];
+            // d softplus = sigmoid(raw) = 1 - exp(-softplus(raw)); series where the difference cancels
+            float spg = 1.f;
+            if (softplus) spg = dv < 1e-2f ? dv * (1.f - dv * (0.5f - dv * (1.f / 6.f))) : 1.f - __expf(-dv);
+            float dzv = 0.f;
             if (has_z) {
               const float zf = Elem<T>::to_f(zv2.v[k]);
               const float sg = sigmoid_fast(zf);
-              dyg = dyf * zf * sg;
               dzv = dyf * fmaf(Dv[k], xf, ys[k]) * sg * (1.f + zf * (1.f - sg));
             }
             const float dxv = fmaf(dyg, Dv[k], dv * gBs[k]);
@@ -441,7 +462,8 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
           }
         }
       }
-      mbar_arrive(&raw_free[j % kStages]);
+      mbar_arrive_relaxed(&op_empty[buf]);
+      mbar_arrive_relaxed(&raw_free[j % kStages]);
     }
 #pragma unroll
     for (int k = 0; k < 2; ++k) {

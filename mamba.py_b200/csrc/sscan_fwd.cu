@@ -35,7 +35,7 @@ namespace {
 template <typename T> struct Ring { static constexpr int kStages = sizeof(T) == 2 ? 8 : 5; };
 constexpr int kTmaProducers = 128;
 constexpr int kTmaThreads = kConsumers + kTmaProducers;
-constexpr int kTile = kChunk;              // timesteps per tile (= carry spacing)
+constexpr int kTile = 2 * kChunk;          // timesteps per tile (two saved states per tile)
 
 struct FwdMaps {
   CUtensorMap x, d, z, B, C;
@@ -123,7 +123,7 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
     const int op_off0 = op_index(0, e_l, kTE), op_off1 = op_index(1, e_l, kTE) - kTE;
     const int yp_off0 = yp_slot<kLPE, kTE>(0, e_l) * kLPE + q;
     const int yp_off1 = yp_slot<kLPE, kTE>(1, e_l) * kLPE + q;
-    float* carry_dst = (p.carries && e_ok) ? p.carries + ((b * ntiles) * p.ED + e) * N + 4 * q : nullptr;
+    float* carry_dst = (p.carries && e_ok) ? p.carries + ((b * ((p.L + kChunk - 1) / kChunk)) * p.ED + e) * N + 4 * q : nullptr;
 
     for (int64_t kt = 0; kt < ntiles; ++kt) {
       const int buf = int(kt & 1);
@@ -131,16 +131,16 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
         atomicExch(&g_fwd_status, MB200_DEV_WAIT_TIMEOUT);
         return;
       }
-      if (carry_dst) {                                  // state entering this 16-step chunk
-        *reinterpret_cast<float4*>(carry_dst) = make_float4(hlo.x, hlo.y, hhi.x, hhi.y);
-        carry_dst += p.ED * N;
-      }
       const float2* op = s_op + buf * kTile * kTE;
       const float* sB = s_B + buf * kTile * N + 4 * q;
       const float* sC = s_C + buf * kTile * N + 4 * q;
       float* yp = s_yp + buf * kTile * kConsumers;
 #pragma unroll
       for (int t = 0; t < kTile; ++t) {
+        if (t % kChunk == 0 && carry_dst && kt * kTile + t < p.L) {     // state entering this chunk
+          *reinterpret_cast<float4*>(carry_dst) = make_float4(hlo.x, hlo.y, hhi.x, hhi.y);
+          carry_dst += p.ED * N;
+        }
         const float2 o = op[t * kTE + ((t & 1) ? op_off1 : op_off0)];   // {delta, delta*x}
         const float4 Bq = *reinterpret_cast<const float4*>(sB + t * N);
         const float4 Cq = *reinterpret_cast<const float4*>(sC + t * N);

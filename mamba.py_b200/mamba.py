@@ -92,11 +92,14 @@ def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None,
     dx = torch.empty((Bsz, L, ED), dtype=x.dtype, device=dev)
     dd = torch.empty_like(dx)
     dz = torch.empty_like(dx) if z is not None else None
-    dB = torch.zeros((Bsz, L, N), dtype=torch.float32, device=dev)
-    dC = torch.zeros_like(dB)
-    dA = torch.zeros((ED, N), dtype=torch.float32, device=dev)
-    dD = torch.zeros((ED,), dtype=torch.float32, device=dev)
-    dbias = torch.zeros((ED,), dtype=torch.float32, device=dev) if delta_bias is not None else None
+    # every buffer the kernel accumulates into comes out of ONE zero-filled allocation (one fill launch)
+    nBC, nA = Bsz * L * N, ED * N
+    acc = torch.zeros(2 * nBC + nA + 2 * ED, dtype=torch.float32, device=dev)
+    dB = acc[:nBC].view(Bsz, L, N)
+    dC = acc[nBC:2 * nBC].view(Bsz, L, N)
+    dA = acc[2 * nBC:2 * nBC + nA].view(ED, N)
+    dD = acc[2 * nBC + nA:2 * nBC + nA + ED]
+    dbias = acc[2 * nBC + nA + ED:] if delta_bias is not None else None
     g_out = torch.empty((Bsz, ED, N), dtype=torch.float32, device=dev) if want_g_out else None
     flags = _lib.DELTA_SOFTPLUS if delta_bias is not None else 0
     zs = (z.stride(0), z.stride(1)) if z is not None else (0, 0)
