@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     for name in _lib.exported_symbols():
         assert name in declared, f"{name} bound in Python but not declared in the header"
     assert lib.mb200_version() >= 100
-    assert lib.mb200_sscan_chunk() == 16
+    assert lib.mb200_sscan_chunk() == 8
 
 
 def test_error_codes_without_a_gpu():
