@@ -1,25 +1,30 @@
 // Fused selective scan, backward.  One pass over x, delta, z, B, C, dy (read once) that writes
 // dx, ddelta, dz and accumulates dB, dC, dA, dD; the hidden states are recomputed chunk by chunk
-// from the states the forward saved every 16 timesteps.
+// from the states the forward saved every kChunk (8) timesteps.
 //
-// Like the forward, the kernel is bound by shared-memory bandwidth and instruction issue, not by
-// HBM, so the recurrences run on warps that do nothing else (tensor-map path, d_state 16; the
-// register-staged kernel in sscan_bwd_generic.cuh covers every other case).
+// The kernel is bound by shared-memory traffic, instruction issue and the latency of each warp's
+// dependent chain, not by HBM, so the recurrences run on warps that do nothing else (tensor-map
+// path, d_state 16; the register-staged kernel in sscan_bwd_generic.cuh covers every other case).
 //
-// A CTA of 256 threads owns 32 channels of one batch row and walks time BACKWARDS in tiles of 16:
+// A CTA of 256 threads owns 32 channels of one batch row and walks time BACKWARDS in tiles of 16
+// (two saved states per tile):
 //   - warp 4 issues TMA loads of the raw x, delta, z, dy, B, C boxes a few tiles ahead into a
 //     shared-memory ring and converts each landed tile into float32 operands
 //     ({softplus(delta+bias), delta*x}, dy*silu(z), B, C; double-buffered).
-//   - warps 0-3 (consumers; a thread owns 4 states of one channel) recompute the states of the
-//     tile forwards from the saved carry, 8 timesteps at a time into registers, and walk them
-//     backwards:  g[t] = dy'[t] C[t] + a[t+1] g[t+1],  da = g h[t-1].  Per timestep a thread
-//     leaves three partial sums over its 4 states (for y, dx, ddelta) and its 8 products for
-//     dB, dC in shared memory, in windows of 2 timesteps.
+//   - warps 0-3 (consumers; a thread owns 4 states of one channel) recompute the 8 states of a
+//     chunk forwards from its saved state into registers and walk them backwards:
+//     g[t] = dy'[t] C[t] + a[t+1] g[t+1],  da = g h[t-1].  Operands of the walk are fetched two
+//     timesteps ahead.  Per timestep a thread leaves three partial sums over its 4 states (for y,
+//     dx, ddelta) and its 8 products for dB, dC in shared memory, in windows of 2 timesteps.
 //   - warps 5 and 7 finish alternate windows: sum the 4 partials of each channel, form dx, ddelta,
-//     dz (and the running sums for dD and d(delta_bias)), store them.
+//     dz (and the running sums for dD and d(delta_bias)), store them.  delta and dy' come from the
+//     operand tile, so only sigmoid(z) and 1 - exp(-delta) are evaluated here.
 //   - warp 6 sums the dB, dC products of each window over the CTA's 32 channels and adds the
 //     result to global memory with vector atomics.
-//   - Hand-off through CTA-local mbarriers; every wait is bounded (see mbar_wait).
+//   - Hand-off through CTA-local mbarriers; every wait is bounded (see mbar_wait).  A barrier's
+//     round trip through the busy shared-memory pipe costs a few hundred cycles, so the consumers
+//     ask for a window's buffer with a non-blocking test before the arithmetic of the window and
+//     only block if the answer was "not yet".
 #include "sscan_bwd_generic.cuh"
 #include "tma.cuh"
 
@@ -170,7 +175,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
       const float2 hp[2] = {make_float2(cv.x, cv.y), make_float2(cv.z, cv.w)};   // state entering the tile
 
       // one forward step of the recurrence from operands in shared memory
-      auto step = [&](int t, float2 (&h)[2], float2 (&av)[2]) {
+      auto step = [&](int t, float2 (&h)[2]) {
         const float2 o = op[t * kBTE + ((t & 1) ? op_off1 : op_off0)];
         const float4 Bq = *reinterpret_cast<const float4*>(sB + t * N);
         const float2 dd = make_float2(o.x, o.x), dxx = make_float2(o.y, o.y);
@@ -178,7 +183,6 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
         const float2 a0 = make_float2(ex2f(e0v.x), ex2f(e0v.y)), a1 = make_float2(ex2f(e1v.x), ex2f(e1v.y));
         h[0] = __ffma2_rn(a0, h[0], __fmul2_rn(dxx, make_float2(Bq.x, Bq.y)));
         h[1] = __ffma2_rn(a1, h[1], __fmul2_rn(dxx, make_float2(Bq.z, Bq.w)));
-        av[0] = a0; av[1] = a1;
       };
       const float2 hmid[2] = {make_float2(cm.x, cm.y), make_float2(cm.z, cm.w)};   // state entering the second half
 
@@ -190,8 +194,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
           float2 h[2] = {half ? hmid[0] : hp[0], half ? hmid[1] : hp[1]};
 #pragma unroll
           for (int i = 0; i < kHalf; ++i) {
-            float2 adrop[2];
-            step(half * kHalf + i, h, adrop);
+            step(half * kHalf + i, h);
             hh[i][0] = h[0]; hh[i][1] = h[1];
           }
         }

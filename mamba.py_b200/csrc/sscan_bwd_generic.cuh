@@ -6,7 +6,7 @@
 // chunk by chunk from the states the forward saved every kChunk timesteps.
 //
 // Mapping: the same as the forward (a thread owns 4 states n of one channel e and walks time
-// serially), but time runs from the last chunk to the first.  For each chunk of 16 timesteps
+// serially), but time runs from the last chunk to the first.  For each chunk of kChunk timesteps
 //   phase R  recomputes a[t] = exp(delta[t] A) and h[t] forwards from the saved state and keeps
 //            both in registers (2 x 16 x 4 floats), so the exponential is evaluated once;
 //   phase B  walks the chunk backwards:  g[t] = dy'[t] C[t] + a[t+1] g[t+1]  and from g, h, a
