@@ -317,8 +317,9 @@ def bench_scan_130m(args, rank, world, dev):
     }
     res["dominant"] = ("sscan_bwd_kernel", bwd_bytes, bwd_ms)
     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of that kernel on this exact workload,
-    # from the ncu capture summarised in profiles/sscan_bwd_kernel__scan_130m.md (306.3 MB + 126.4 MB)
-    res["traffic"] = 432.7e6
+    # from the ncu capture summarised in profiles/sscan_bwd_kernel__scan_130m.md (406.6 MB + 132.9 MB;
+    # 354.4 MB algorithmic plus 201 MB of saved scan states read back)
+    res["traffic"] = 539.5e6
 
     if args.skip_e2e:
         sampler.stop()
