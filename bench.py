@@ -239,8 +239,9 @@ def run_reference(args, rank):
 
 
 METRIC = {"scan_130m": "selective_scan_fwd_bwd_tokens_per_s", "lshard": "selective_scan_fwd_bwd_tokens_per_s",
-          "pscan": "pscan_fwd_bwd_tokens_per_s", "decode": "decode_layer_steps_tokens_per_s"}
-SCALING = {"scan_130m": "weak", "pscan": "weak", "decode": "weak", "lshard": "strong"}
+          "pscan": "pscan_fwd_bwd_tokens_per_s", "decode": "decode_layer_steps_tokens_per_s",
+          "layer": "mamba_layer_fwd_bwd_tokens_per_s"}
+SCALING = {"scan_130m": "weak", "pscan": "weak", "decode": "weak", "lshard": "strong", "layer": "weak"}
 
 
 def workload_config(wl, n):
@@ -258,6 +259,12 @@ def workload_config(wl, n):
                 "B_per_gpu": 256, "global_batch": 256 * n, "ED": 5120, "N": 16, "io_dtype": "bf16",
                 "state_dtype": "f32", "parallelism": f"batch-sharded x{n}, no collective",
                 "l2": "8 layers' states (0.67 GB) are cycled so every step misses L2"}
+    if wl == "layer":
+        return {"workload": "one whole Mamba-130m-shaped layer fwd+bwd (projections by the GEMM library, conv1d+SiLU "
+                            "and gated scan by this library), bf16 autocast, float32 scan state",
+                "B_per_gpu": 8, "global_batch": 8 * n, "seq_len": 2048, "d_model": 768, "ED": 1536, "N": 16,
+                "io_dtype": "bf16", "state_dtype": "f32", "parallelism": f"batch-sharded x{n}, no collective",
+                "l2": "activations of one step exceed the 126 MB L2; no flush needed"}
     return {"workload": "L-sharded fused selective scan fwd+bwd, long sequence", "global_batch": 1,
             "seq_len": 131072, "ED": 5120, "N": 16, "io_dtype": "bf16", "state_dtype": "f32",
             "parallelism": f"sequence split over {n} GPU(s), carry all-gather over NCCL",
@@ -462,7 +469,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="scan_130m", choices=["scan_130m", "pscan", "decode", "lshard"])
+    ap.add_argument("--workload", default="scan_130m", choices=["scan_130m", "pscan", "decode", "lshard", "layer"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
     args = ap.parse_args()
@@ -492,6 +499,9 @@ def main():
     elif wl == "decode":
         from mamba_b200.benchmarks import bench_decode
         res = bench_decode(args, rank, world, dev, ClockSampler, time_region, time_kernel)
+    elif wl == "layer":
+        from mamba_b200.benchmarks import bench_layer
+        res = bench_layer(args, rank, world, dev, ClockSampler, time_region, time_kernel)
     else:
         from mamba_b200.benchmarks import bench_lshard
         res = bench_lshard(args, rank, world, dev, ClockSampler, time_region, time_kernel)

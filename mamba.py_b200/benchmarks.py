@@ -240,3 +240,79 @@ def bench_lshard(args, rank, world, dev, ClockSampler, time_region, time_kernel)
                       "steps": 3, "ms_per_step": ems / 3,
                       "note": f"first {n} timesteps of each rank's shard per step"}
     return res
+
+
+def bench_layer(args, rank, world, dev, ClockSampler, time_region, time_kernel):
+    """One whole Mamba-130m-shaped layer, forward + backward, bf16 autocast with float32 scan state:
+    in_proj, conv1d+SiLU kernel, x_proj, dt_proj, fused scan (softplus, gate inside), out_proj.
+    The four projections are library GEMMs; the line reports how the step splits."""
+    from . import mamba as M
+    Bsz, L, d_model = 8, 2048, 768
+    layer = workloads.LayerParams(1002 + rank, dev, d_model=d_model)
+    gen = torch.Generator(device=dev).manual_seed(77 + rank)
+    x = torch.randn(Bsz, L, d_model, generator=gen, device=dev).requires_grad_()
+    dy = torch.randn(Bsz, L, d_model, generator=gen, device=dev)
+    params = list(layer.parameters())
+
+    def step():
+        x.grad = None
+        for q in params:
+            q.grad = None
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            y = M.forward(layer, x)
+        y.backward(dy.to(y.dtype))
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(dev.index or 0)
+    sampler.start()
+    ms, t_lo, t_hi = time_region(step, args.steps, world)
+    res = {"value": Bsz * L * world * args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
+           "gpu_launches": 4 * args.steps}
+
+    # the library's own kernels alone, on the tensors the layer really feeds them
+    with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+        xz = layer.in_proj(x)
+        xs, z = xz.chunk(2, dim=-1)
+        xc = M.causal_conv1d_silu(xs, layer.conv1d.weight, layer.conv1d.bias)
+        dlt, Bm, Cm = M._project(layer, xc)
+        draw = torch.nn.functional.linear(dlt, layer.dt_proj.weight)
+    A = -torch.exp(layer.A_log.detach().float())
+    D, bias = layer.D.detach().float(), layer.dt_proj.bias.detach().float()
+    gy = torch.randn(Bsz, L, 2 * d_model, generator=gen, device=dev).to(torch.bfloat16)
+    keep = {}
+
+    def fwd():
+        keep["o"] = M.sscan_fwd_raw(xc, draw, A, Bm, Cm, D, z, bias, want_carries=True)
+
+    fwd()
+
+    def bwd():
+        keep["g"] = M.sscan_bwd_raw(xc, draw, A, Bm, Cm, D, z, bias, gy, keep["o"][2])
+
+    xs_leaf = xs.detach().requires_grad_()
+
+    def conv_fb():
+        xs_leaf.grad = None
+        M.causal_conv1d_silu(xs_leaf, layer.conv1d.weight.detach(), layer.conv1d.bias.detach()).backward(gy)
+
+    for f in (fwd, bwd, conv_fb, fwd, bwd, conv_fb):
+        f()
+    fwd_ms, fwd_min = time_kernel(fwd, 20)
+    bwd_ms, bwd_min = time_kernel(bwd, 20)
+    conv_ms, conv_min = time_kernel(conv_fb, 20)
+    sampler.stop()
+    ED, N = 2 * d_model, 16
+    fwd_bytes = (4 * ED + 2 * N) * 2 * Bsz * L
+    bwd_bytes = (7 * ED + 4 * N) * 2 * Bsz * L
+    res["kernels"] = {
+        "sscan_fwd_kernel": {"ms": fwd_ms, "ms_min": fwd_min, "algorithmic_bytes": fwd_bytes,
+                             "GBps": fwd_bytes / fwd_ms / 1e6},
+        "sscan_bwd_kernel": {"ms": bwd_ms, "ms_min": bwd_min, "algorithmic_bytes": bwd_bytes,
+                             "GBps": bwd_bytes / bwd_ms / 1e6},
+        "conv1d_silu_fwd+bwd": {"ms": conv_ms, "ms_min": conv_min},
+        "projections_and_glue": {"ms": ms / args.steps - fwd_ms - bwd_ms - conv_ms},
+    }
+    res["dominant"] = ("sscan_bwd_kernel", bwd_bytes, bwd_ms)
+    res["clocks"] = sampler.summary(t_lo, t_hi)
+    return res

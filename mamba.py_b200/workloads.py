@@ -11,6 +11,8 @@ charts use random tensors.  Every generator takes a seed and a device and return
   pscan_inputs             A_in = exp(-softplus(N(0,1))) in (0,1), X_in ~ N(0,1), grad ~ N(0,1)
   long_scan_inputs         the long-sequence config: delta = softplus(N(0,1)*0.5 - 4.6), the rest N(0,1)
   decode_layer_weights     weights and caches of one Mamba-2.8b-shaped layer for step()
+  LayerParams              the parameters of one MambaBlock-shaped layer under the reference's
+                           attribute names, for timing the whole layer (projections included)
 """
 from __future__ import annotations
 
@@ -116,3 +118,37 @@ def decode_layer_weights(seed: int, device, d_model=2560, N=16, d_conv=4, dtype=
         D=torch.ones(ED, device=device),
         out_proj=u((d_model, ED), 1 / math.sqrt(ED)).to(dtype),
     )
+
+
+class LayerParams(torch.nn.Module):
+    """The parameters of one Mamba layer under the attribute names of the reference's MambaBlock
+    (mambapy/mamba.py:127-172: in_proj, conv1d, x_proj, dt_proj, A_log, D, out_proj, config), with its
+    initialisation (dt bias inverse-softplus of log-uniform dt, S4D-real A).  It holds parameters only;
+    `mamba_b200.mamba.forward(params, x)` runs the layer."""
+
+    def __init__(self, seed: int, device, d_model=768, N=16, d_conv=4, expand=2):
+        super().__init__()
+        import types
+        nn = torch.nn
+        ED, R = expand * d_model, math.ceil(d_model / 16)
+        self.config = types.SimpleNamespace(d_model=d_model, d_inner=ED, dt_rank=R, d_state=N, d_conv=d_conv)
+        gen = torch.Generator(device=device).manual_seed(seed)
+        u = lambda shape, bound: (torch.rand(shape, generator=gen, device=device) * 2 - 1) * bound
+        self.in_proj = nn.Linear(d_model, 2 * ED, bias=False, device=device)
+        self.conv1d = nn.Conv1d(ED, ED, d_conv, groups=ED, padding=d_conv - 1, bias=True, device=device)
+        self.x_proj = nn.Linear(ED, R + 2 * N, bias=False, device=device)
+        self.dt_proj = nn.Linear(R, ED, bias=True, device=device)
+        self.out_proj = nn.Linear(ED, d_model, bias=False, device=device)
+        with torch.no_grad():
+            self.in_proj.weight.copy_(u((2 * ED, d_model), 1 / math.sqrt(d_model)))
+            self.conv1d.weight.copy_(u((ED, 1, d_conv), 1 / math.sqrt(d_conv)))
+            self.conv1d.bias.copy_(u((ED,), 1 / math.sqrt(d_conv)))
+            self.x_proj.weight.copy_(u((R + 2 * N, ED), 1 / math.sqrt(ED)))
+            self.dt_proj.weight.copy_(u((ED, R), R ** -0.5))
+            self.dt_proj.bias.copy_(dt_bias_init(ED, gen, device))
+            self.out_proj.weight.copy_(u((d_model, ED), 1 / math.sqrt(ED)))
+        self.A_log = nn.Parameter(torch.log(torch.arange(1, N + 1, dtype=torch.float32, device=device)).repeat(ED, 1))
+        self.D = nn.Parameter(torch.ones(ED, device=device))
+
+    def _apply_layernorms(self, dt, B, C):
+        return dt, B, C
