@@ -108,13 +108,6 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar))
                : "memory");
 }
-// Arrival that only says "I have finished READING what this barrier guards" (the values read have
-// already been consumed by earlier instructions).  It orders nothing, so it does not wait for the
-// thread's outstanding global stores or reductions the way a releasing arrive does.
-__device__ __forceinline__ void mbar_arrive_relaxed(uint64_t* bar) {
-  asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.relaxed.cta.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar))
-               : "memory");
-}
 // true when the phase with the given parity has completed; false after kSpinLimit polls.
 // A pending poll is followed by a short sleep: a waiting warp must not spend issue slots and
 // shared-memory bandwidth (the poll is a shared-memory access) that the working warps need.

@@ -376,7 +376,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
           acc0 = __fadd2_rn(acc0, *reinterpret_cast<const float2*>(src + 4 * ((k + which) & (kBTE - 1))));
           acc1 = __fadd2_rn(acc1, *reinterpret_cast<const float2*>(src + 4 * ((k + 1 + which) & (kBTE - 1))));
         }
-        mbar_arrive_relaxed(&win_empty[wb]);
+        mbar_arrive(&win_empty[wb]);
         const int64_t t = t0 + win_t(wl) + ti;
         if (t < p.L) red_add_v2(gbase + t * N, acc0.x + acc1.x, acc0.y + acc1.y);
       }
@@ -419,7 +419,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
           gBs[k] = (v1.x + v1.y) + (v1.z + v1.w);
           wAs[k] = (v2.x + v2.y) + (v2.z + v2.w);
         }
-        mbar_arrive_relaxed(&win_empty[par]);
+        mbar_arrive(&win_empty[par]);
         const int tt = win_t(wl) + ti;                   // timestep inside the tile
         const int64_t t = t0 + tt;
         if (t < p.L && c0 < cols_ok) {
@@ -465,8 +465,8 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
           }
         }
       }
-      mbar_arrive_relaxed(&op_empty[buf]);
-      mbar_arrive_relaxed(&raw_free[j % kStages]);
+      mbar_arrive(&op_empty[buf]);
+      mbar_arrive(&raw_free[j % kStages]);
     }
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
