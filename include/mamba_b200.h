@@ -233,6 +233,21 @@ int mb200_decay_prod(const void* delta, const float* A, const float* delta_bias,
                      int64_t B, int64_t L, int64_t ED, int N,
                      int64_t d_sb, int64_t d_sl, int dtype, int flags, void* stream);
 
+/* ---- RMSNorm over the last dimension (mambapy/mamba.py:416-433, used in front of every block at
+ * mambapy/mamba.py:111 and for the optional inner normalisation of delta, B, C):
+ *   y[r, d] = x[r, d] * rsqrt(mean_d x[r, :]^2 + eps) * weight[d]      (weight NULL = no gain, the muP case)
+ * x, y: `rows` rows of D activations, last dimension unit-stride, row strides in elements; arithmetic is
+ * float32.  rstd (rows) float32, optional: the per-row rsqrt, which mb200_rmsnorm_bwd needs. */
+int mb200_rmsnorm_fwd(const void* x, const float* weight, void* y, float* rstd, int64_t rows, int64_t D,
+                      int64_t x_rs, int64_t y_rs, float eps, int dtype, void* stream);
+
+/* Backward of mb200_rmsnorm_fwd (what autograd derives for mambapy/mamba.py:427-433).
+ * dx out (activation dtype); dweight (D) float32 or NULL, ACCUMULATED into (caller zero-fills);
+ * D <= 12288 when dweight is given (MB200_ETOOBIG otherwise). */
+int mb200_rmsnorm_bwd(const void* x, const float* weight, const float* rstd, const void* dy, void* dx,
+                      float* dweight, int64_t rows, int64_t D, int64_t x_rs, int64_t dy_rs, int64_t dx_rs,
+                      int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

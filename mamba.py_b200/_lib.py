@@ -33,6 +33,8 @@ _SIGNATURES = {
     "mb200_conv_step": (_int, [_ptr] * 6 + [_i64] * 2 + [_int, _i64, _int, _ptr]),
     "mb200_conv1d_silu_fwd": (_int, [_ptr] * 4 + [_i64] * 3 + [_int] + [_i64] * 4 + [_int, _ptr]),
     "mb200_conv1d_silu_bwd": (_int, [_ptr] * 7 + [_i64] * 3 + [_int] + [_i64] * 6 + [_int, _ptr]),
+    "mb200_rmsnorm_fwd": (_int, [_ptr] * 4 + [_i64] * 4 + [C.c_float, _int, _ptr]),
+    "mb200_rmsnorm_bwd": (_int, [_ptr] * 6 + [_i64] * 5 + [_int, _ptr]),
     "mb200_carry_fold": (_int, [_ptr] * 3 + [_i64] * 2 + [_int, _int, _ptr]),
     "mb200_decay_prod": (_int, [_ptr] * 4 + [_i64] * 3 + [_int] + [_i64] * 2 + [_int, _int, _ptr]),
 }

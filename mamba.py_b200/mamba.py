@@ -291,6 +291,61 @@ def causal_conv1d_silu(x, weight, bias=None):
     return CausalConv1dSiluFn.apply(x, weight, bias)
 
 
+class RMSNormFn(torch.autograd.Function):
+    """y = x * rsqrt(mean(x^2, -1) + eps) * weight in one pass over x (mambapy/mamba.py:416-433)."""
+
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        lib = _lib.load()
+        dt = _act_dtype(x)
+        D = x.shape[-1]
+        x2 = x.reshape(-1, D)
+        if x2.dtype != dt or x2.stride(-1) != 1:
+            x2 = x2.to(dt).contiguous()
+        rows = x2.shape[0]
+        w32 = None if weight is None else _f32(weight)
+        y = torch.empty((rows, D), dtype=dt, device=x.device)
+        rstd = torch.empty((rows,), dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            rc = lib.mb200_rmsnorm_fwd(x2.data_ptr(), _lib.ptr(w32), y.data_ptr(), rstd.data_ptr(), rows, D,
+                                       x2.stride(0), y.stride(0), float(eps), _lib.dtype_code(dt),
+                                       _lib.current_stream(x.device))
+        _lib.check(rc, "mb200_rmsnorm_fwd")
+        ctx.save_for_backward(x2, w32, rstd)
+        ctx.meta = (x.shape, x.dtype, None if weight is None else weight.dtype)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w32, rstd = ctx.saved_tensors
+        shape, tx, tw = ctx.meta
+        lib = _lib.load()
+        rows, D = x2.shape
+        dy2 = dy.reshape(rows, D)
+        if dy2.dtype != x2.dtype or dy2.stride(-1) != 1:
+            dy2 = dy2.to(x2.dtype).contiguous()
+        dx = torch.empty_like(x2)
+        dw = torch.zeros(D, dtype=torch.float32, device=x2.device) if w32 is not None else None
+        with torch.cuda.device(x2.device):
+            rc = lib.mb200_rmsnorm_bwd(x2.data_ptr(), _lib.ptr(w32), rstd.data_ptr(), dy2.data_ptr(), dx.data_ptr(),
+                                       _lib.ptr(dw), rows, D, x2.stride(0), dy2.stride(0), dx.stride(0),
+                                       _lib.dtype_code(x2.dtype), _lib.current_stream(x2.device))
+        _lib.check(rc, "mb200_rmsnorm_bwd")
+        return dx.view(shape).to(tx), None if dw is None else dw.to(tw), None
+
+
+def rms_norm(x, weight=None, eps=1e-5):
+    """RMSNorm over the last dimension; weight None is the reference's muP variant (no gain)."""
+    if not x.is_cuda:
+        raise RuntimeError("mamba_b200 kernels need CUDA tensors; there is no CPU path")
+    return RMSNormFn.apply(x, weight, eps)
+
+
+def rmsnorm_forward(self, x):
+    """Drop-in for RMSNorm.forward (mambapy/mamba.py:427-433)."""
+    return rms_norm(x, None if self.use_mup else self.weight, self.eps)
+
+
 def _project(self, x):
     """delta (pre-softplus, without bias), B, C from x as in mambapy/mamba.py:393-396."""
     cfg = self.config

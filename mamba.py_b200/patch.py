@@ -35,7 +35,7 @@ def install(fuse_block: bool = False) -> None:
     fuse_block=False keeps MambaBlock.forward/ssm as they are and swaps only the methods whose
     signatures the reference defines (selective_scan, selective_scan_seq, ssm_step, step) plus
     pscan/PScan.  fuse_block=True also swaps MambaBlock.ssm and MambaBlock.forward for the
-    variants that run softplus, scan and gate in one kernel.
+    variants that run softplus, scan and gate in one kernel, and RMSNorm.forward for the one-pass kernel.
     """
     if _saved:
         return
@@ -61,6 +61,9 @@ def install(fuse_block: bool = False) -> None:
     if fuse_block:
         _swap(blocks[0], "ssm", _m.ssm)
         _swap(blocks[0], "forward", _m.forward)
+        norm = getattr(sys.modules["mambapy.mamba"], "RMSNorm", None)
+        if norm is not None:
+            _swap(norm, "forward", _m.rmsnorm_forward)
 
 
 def uninstall() -> None:

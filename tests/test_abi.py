@@ -91,7 +91,10 @@ def test_install_rebinds_reference_names_and_uninstall_restores():
         mamba_b200.uninstall()
         mamba_b200.install(fuse_block=True)
         assert rm.MambaBlock.forward is not orig[7]
+        norm_fwd = rm.RMSNorm.forward
+        assert norm_fwd.__name__ == "rmsnorm_forward"
         mamba_b200.uninstall()
+        assert rm.RMSNorm.forward is not norm_fwd
         now = (rp.pscan, rp.PScan, rm.pscan, rm.MambaBlock.selective_scan, rm.MambaBlock.step,
                rm.MambaBlock.ssm_step, rm.MambaBlock.selective_scan_seq, rm.MambaBlock.forward)
         assert all(a is b for a, b in zip(orig, now)) and not mamba_b200.installed()
