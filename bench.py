@@ -260,8 +260,8 @@ def workload_config(wl, n):
                 "state_dtype": "f32", "parallelism": f"batch-sharded x{n}, no collective",
                 "l2": "8 layers' states (0.67 GB) are cycled so every step misses L2"}
     if wl == "layer":
-        return {"workload": "one whole Mamba-130m-shaped layer fwd+bwd (projections by the GEMM library, conv1d+SiLU "
-                            "and gated scan by this library), bf16 autocast, float32 scan state",
+        return {"workload": "one whole Mamba-130m-shaped residual layer fwd+bwd (projections by the GEMM library; RMSNorm, "
+                            "conv1d+SiLU and gated scan by this library), bf16 autocast, float32 scan state",
                 "B_per_gpu": 8, "global_batch": 8 * n, "seq_len": 2048, "d_model": 768, "ED": 1536, "N": 16,
                 "io_dtype": "bf16", "state_dtype": "f32", "parallelism": f"batch-sharded x{n}, no collective",
                 "l2": "activations of one step exceed the 126 MB L2; no flush needed"}

@@ -36,13 +36,22 @@ enum {
   MB200_EALIGN = -4,      /* a float32 state/carry pointer is not 16-byte aligned */
   MB200_ELAUNCH = -5,     /* the CUDA runtime refused the launch                  */
   MB200_ETOOBIG = -6,     /* size beyond a documented limit of the entry point    */
-  MB200_ESETUP = -7       /* per-device set-up of the library failed              */
+  MB200_ESETUP = -7,      /* per-device set-up of the library failed              */
+  MB200_EUNSUPPORTED = -8 /* the option is not available for these tensors (see the entry point) */
 };
 
 /* Flags of mb200_sscan_fwd / mb200_sscan_bwd. */
 enum {
-  MB200_DELTA_SOFTPLUS = 1  /* delta = softplus(delta_raw + delta_bias[e]) is applied inside;
+  MB200_DELTA_SOFTPLUS = 1, /* delta = softplus(delta_raw + delta_bias[e]) is applied inside;
                                without it `delta` is taken as already discretised           */
+  MB200_REVERSE = 2         /* scan from t = L-1 down to 0 (h[t] = a[t] h[t+1] + ...): what the
+                               reference's bidirectional model gets by flipping the sequence,
+                               scanning and flipping back (mambapy/vim.py:228-261).  h0 is then the
+                               state entering t = L-1, hT the one leaving t = 0, and entry c of
+                               `carries` the state entering time chunk c from the right.  Served
+                               only by the tensor-map path (16-byte aligned bases and strides;
+                               backward: d_state 16); otherwise MB200_EUNSUPPORTED is returned
+                               and the caller flips the tensors itself.                     */
 };
 
 const char* mb200_strerror(int code);

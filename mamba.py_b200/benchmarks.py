@@ -243,9 +243,10 @@ def bench_lshard(args, rank, world, dev, ClockSampler, time_region, time_kernel)
 
 
 def bench_layer(args, rank, world, dev, ClockSampler, time_region, time_kernel):
-    """One whole Mamba-130m-shaped layer, forward + backward, bf16 autocast with float32 scan state:
-    in_proj, conv1d+SiLU kernel, x_proj, dt_proj, fused scan (softplus, gate inside), out_proj.
-    The four projections are library GEMMs; the line reports how the step splits."""
+    """One whole Mamba-130m-shaped residual layer (mambapy/mamba.py:111), forward + backward, bf16 autocast
+    with float32 scan state: RMSNorm kernel, in_proj, conv1d+SiLU kernel, x_proj, dt_proj, fused scan
+    (softplus, gate inside), out_proj, residual add.  The four projections are library GEMMs; the line
+    reports how the step splits."""
     from . import mamba as M
     Bsz, L, d_model = 8, 2048, 768
     layer = workloads.LayerParams(1002 + rank, dev, d_model=d_model)
@@ -259,7 +260,7 @@ def bench_layer(args, rank, world, dev, ClockSampler, time_region, time_kernel):
         for q in params:
             q.grad = None
         with torch.autocast("cuda", dtype=torch.bfloat16):
-            y = M.forward(layer, x)
+            y = M.forward(layer, M.rms_norm(x, layer.norm_weight, 1e-5)) + x
         y.backward(dy.to(y.dtype))
 
     for _ in range(max(args.warmup, 3)):
@@ -272,7 +273,7 @@ def bench_layer(args, rank, world, dev, ClockSampler, time_region, time_kernel):
 
     # the library's own kernels alone, on the tensors the layer really feeds them
     with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
-        xz = layer.in_proj(x)
+        xz = layer.in_proj(M.rms_norm(x, layer.norm_weight, 1e-5))
         xs, z = xz.chunk(2, dim=-1)
         xc = M.causal_conv1d_silu(xs, layer.conv1d.weight, layer.conv1d.bias)
         dlt, Bm, Cm = M._project(layer, xc)

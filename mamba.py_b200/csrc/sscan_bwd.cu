@@ -78,7 +78,7 @@ __device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
   asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
 }
 
-template <typename T>
+template <typename T, bool kRev>
 __global__ void __launch_bounds__(kBwdThreads, 3)
 sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams p) {
   using S = TmaBwdSmem<T>;
@@ -109,6 +109,13 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
   const bool softplus = (p.flags & MB200_DELTA_SOFTPLUS) != 0;
   const bool has_z = p.z != nullptr;
   const int64_t ntiles = (p.L + kBTile - 1) / kBTile;
+  // Direction of the scan being differentiated (MB200_REVERSE: it ran from t = L-1 down to 0).  Tiles
+  // are taken in the opposite order of that scan: iteration j works on the tile that starts at
+  // tile_t0(j); step s of a tile in the scan's own order is its row `row(s)`.  Saved states are
+  // indexed by time chunk: entry c is the state entering chunk c in the scan direction.
+  constexpr bool rev = kRev;
+  auto tile_t0 = [&](int64_t j) { return (rev ? j : ntiles - 1 - j) * kBTile; };
+  auto row = [](int s) { return rev ? kBTile - 1 - s : s; };
 
   if (tid == 0) {
 #pragma unroll
@@ -160,13 +167,18 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
       return (e_ok && c < nchunks) ? *reinterpret_cast<const float4*>(carry_base + c * p.ED * N)
                                    : make_float4(0.f, 0.f, 0.f, 0.f);
     };
-    float4 carry_next = load_carry(2 * (ntiles - 1)), carry_next_mid = load_carry(2 * (ntiles - 1) + 1);
+    // states entering the first / second half (in scan order) of iteration j's tile
+    // (time chunk 2*tile + 1 is the first half in scan order when reversed, chunk 2*tile otherwise)
+    float4 carry_next = load_carry(rev ? 1 : 2 * (ntiles - 1)), carry_next_mid = load_carry(rev ? 0 : 2 * (ntiles - 1) + 1);
 
     for (int64_t j = 0; j < ntiles; ++j) {
-      const int64_t kt = ntiles - 1 - j;
       const int buf = int(j & 1);
       const float4 cv = carry_next, cm = carry_next_mid;
-      if (kt > 0) { carry_next = load_carry(2 * kt - 2); carry_next_mid = load_carry(2 * kt - 1); }
+      if (j + 1 < ntiles) {                               // the next tile's two states, a tile ahead
+        const int64_t c = rev ? 2 * j + 2 : 2 * (ntiles - 2 - j);
+        carry_next = load_carry(rev ? c + 1 : c);
+        carry_next_mid = load_carry(rev ? c : c + 1);
+      }
       if (!mbar_wait(&op_full[buf], int((j >> 1) & 1))) { fail(); return; }
       const float2* op = s_op + buf * kBTile * kBTE;
       const float* dyp = s_dyp + buf * kBTile * kBTE + e_l;
@@ -175,7 +187,8 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
       const float2 hp[2] = {make_float2(cv.x, cv.y), make_float2(cv.z, cv.w)};   // state entering the tile
 
       // one forward step of the recurrence from operands in shared memory
-      auto step = [&](int t, float2 (&h)[2]) {
+      auto step = [&](int s, float2 (&h)[2]) {
+        const int t = row(s);
         const float2 o = op[t * kBTE + ((t & 1) ? op_off1 : op_off0)];
         const float4 Bq = *reinterpret_cast<const float4*>(sB + t * N);
         const float2 dd = make_float2(o.x, o.x), dxx = make_float2(o.y, o.y);
@@ -201,7 +214,8 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
         // operands of the reverse walk are fetched one timestep ahead, so that their trip through the
         // shared-memory pipe overlaps the previous timestep's arithmetic, stores and barrier traffic
         struct Opnd { float2 o; float dy; float4 B, C; };
-        auto fetch = [&](int t) {
+        auto fetch = [&](int s) {
+          const int t = row(s);
           Opnd r;
           r.o = op[t * kBTE + ((t & 1) ? op_off1 : op_off0)];
           r.dy = dyp[t * kBTE];
@@ -282,7 +296,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
       const int r = int(j % kStages);
       if (j >= kStages && !mbar_wait(&raw_free[r], int((j / kStages - 1) & 1))) return false;
       unsigned char* st = stage_ptr(j);
-      const int t0 = int((ntiles - 1 - j) * kBTile);
+      const int t0 = int(tile_t0(j));
       mbar_expect_tx(&raw_full[r], stage_tx);
       tma_load_3d(st, &maps.x, int(e0), t0, int(b), &raw_full[r]);
       tma_load_3d(st + S::kActBytes, &maps.d, int(e0), t0, int(b), &raw_full[r]);
@@ -298,7 +312,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
     }
     for (int64_t j = 0; j < ntiles; ++j) {
       const int buf = int(j & 1);
-      const int rows_ok = int(min64(kBTile, p.L - (ntiles - 1 - j) * kBTile));
+      const int rows_ok = int(min64(kBTile, p.L - tile_t0(j)));
       if (j >= 2 && !mbar_wait(&op_empty[buf], int(((j - 2) >> 1) & 1))) { fail(); return; }
       if (!mbar_wait(&raw_full[j % kStages], int((j / kStages) & 1))) { fail(); return; }
       const unsigned char* st = stage_ptr(j);
@@ -360,7 +374,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
     const int ti = lane >> 4, which = (lane >> 3) & 1, qq = (lane >> 1) & 3, hf = lane & 1;
     float* gbase = (which ? p.dC : p.dB) + b * p.L * N + 4 * qq + 2 * hf;
     for (int64_t j = 0; j < ntiles; ++j) {
-      const int64_t t0 = (ntiles - 1 - j) * kBTile;
+      const int64_t t0 = tile_t0(j);
 #pragma unroll 1
       for (int wl = 0; wl < kWinsPerTile; ++wl) {
         const int64_t wseq = j * kWinsPerTile + wl;
@@ -377,7 +391,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
           acc1 = __fadd2_rn(acc1, *reinterpret_cast<const float2*>(src + 4 * ((k + 1 + which) & (kBTE - 1))));
         }
         mbar_arrive(&win_empty[wb]);
-        const int64_t t = t0 + win_t(wl) + ti;
+        const int64_t t = t0 + row(win_t(wl) + ti);
         if (t < p.L) red_add_v2(gbase + t * N, acc0.x + acc1.x, acc0.y + acc1.y);
       }
     }
@@ -394,7 +408,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
     const float Dv[2] = {s_D[c0], s_D[c0 + 1]};
     float dDacc[2] = {0.f, 0.f}, dbacc[2] = {0.f, 0.f};
     for (int64_t j = 0; j < ntiles; ++j) {
-      const int64_t t0 = (ntiles - 1 - j) * kBTile;
+      const int64_t t0 = tile_t0(j);
       if (!mbar_wait(&raw_full[j % kStages], int((j / kStages) & 1))) { fail(); return; }
       const unsigned char* st = stage_ptr(j);
       const T* rx = reinterpret_cast<const T*>(st);
@@ -420,7 +434,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
           wAs[k] = (v2.x + v2.y) + (v2.z + v2.w);
         }
         mbar_arrive(&win_empty[par]);
-        const int tt = win_t(wl) + ti;                   // timestep inside the tile
+        const int tt = row(win_t(wl) + ti);              // row inside the tile
         const int64_t t = t0 + tt;
         if (t < p.L && c0 < cols_ok) {
           const Vec2<T> xv = *reinterpret_cast<const Vec2<T>*>(rx + tt * kBTE + c0);
@@ -497,7 +511,7 @@ int bwd_tma_launch(const SscanBwdParams& p, cudaStream_t st) {
   if (ok && p.z) ok = tma_encode(&m.z, p.z, bf, p.B, p.L, p.ED, p.z_sb, p.z_sl, kBTE, kBTile);
   else if (ok) m.z = m.x;
   if (!ok) return 1;                                   // caller falls back to the generic path
-  auto k = sscan_bwd_tma_kernel<T>;
+  auto k = (p.flags & MB200_REVERSE) ? sscan_bwd_tma_kernel<T, true> : sscan_bwd_tma_kernel<T, false>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess)
     return MB200_ELAUNCH;
   dim3 grid(unsigned((p.ED + kBTE - 1) / kBTE), unsigned(p.B));
@@ -576,6 +590,7 @@ extern "C" int mb200_sscan_bwd(const void* x, const void* delta, const void* z, 
     const int rc = dtype == MB200_F32 ? bwd_tma_launch<float>(p, st) : bwd_tma_launch<__nv_bfloat16>(p, st);
     if (rc <= 0) return rc;
   }
+  if (flags & MB200_REVERSE) return MB200_EUNSUPPORTED;   // the reverse direction exists on the tensor-map path only
   const int kv = dtype == MB200_F32 ? 4 : 8;
   bool vec = ED % kv == 0;
   for (const void* q : {x, delta, z, Bm, Cm, dy, (const void*)dx, (const void*)ddelta, (const void*)dz})

@@ -61,7 +61,7 @@ template <typename T, int N> struct TmaFwdSmem {
   static constexpr int kBytes = kBars + (2 * kStages + 4) * 8;
 };
 
-template <typename T, int N>
+template <typename T, int N, bool kRev>
 __global__ void __launch_bounds__(kTmaThreads, 3)
 sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams p) {
   using G = SscanGeom<N>;
@@ -89,6 +89,12 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
   const bool has_y = p.y != nullptr;
   const bool has_z = p.z != nullptr;
   const int64_t ntiles = (p.L + kTile - 1) / kTile;
+  // Direction.  With MB200_REVERSE time is walked from L-1 down to 0: processing tile kt is the
+  // tile of timesteps starting at tile_t0(kt), and processing step s of a tile is its row 15 - s.
+  // Saved states are indexed by TIME chunk either way: entry c is the state entering chunk c in the
+  // scan direction.
+  constexpr bool rev = kRev;
+  auto tile_t0 = [&](int64_t kt) { return (rev ? ntiles - 1 - kt : kt) * kTile; };
 
   if (tid == 0) {
 #pragma unroll
@@ -123,7 +129,11 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
     const int op_off0 = op_index(0, e_l, kTE), op_off1 = op_index(1, e_l, kTE) - kTE;
     const int yp_off0 = yp_slot<kLPE, kTE>(0, e_l) * kLPE + q;
     const int yp_off1 = yp_slot<kLPE, kTE>(1, e_l) * kLPE + q;
-    float* carry_dst = (p.carries && e_ok) ? p.carries + ((b * ((p.L + kChunk - 1) / kChunk)) * p.ED + e) * N + 4 * q : nullptr;
+    const int64_t nchunks = (p.L + kChunk - 1) / kChunk;
+    float* carry_base = (p.carries && e_ok) ? p.carries + (b * nchunks * p.ED + e) * N + 4 * q : nullptr;
+    // row of processing step t is rb0 + t * rstep (in operand-tile rows); odd rows use the other swizzle offset
+    constexpr int rb0 = rev ? kTile - 1 : 0, rstep = rev ? -1 : 1;
+    const int off_even = rev ? op_off1 : op_off0, off_odd = rev ? op_off0 : op_off1;
 
     for (int64_t kt = 0; kt < ntiles; ++kt) {
       const int buf = int(kt & 1);
@@ -131,19 +141,22 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
         atomicExch(&g_fwd_status, MB200_DEV_WAIT_TIMEOUT);
         return;
       }
+      const int64_t t0a = tile_t0(kt);
       const float2* op = s_op + buf * kTile * kTE;
       const float* sB = s_B + buf * kTile * N + 4 * q;
       const float* sC = s_C + buf * kTile * N + 4 * q;
       float* yp = s_yp + buf * kTile * kConsumers;
 #pragma unroll
       for (int t = 0; t < kTile; ++t) {
-        if (t % kChunk == 0 && carry_dst && kt * kTile + t < p.L) {     // state entering this chunk
-          *reinterpret_cast<float4*>(carry_dst) = make_float4(hlo.x, hlo.y, hhi.x, hhi.y);
-          carry_dst += p.ED * N;
+        if (t % kChunk == 0 && carry_base) {                              // state entering this chunk
+          const int64_t c = t0a / kChunk + (rev ? 1 - t / kChunk : t / kChunk);
+          if (c < nchunks)
+            *reinterpret_cast<float4*>(carry_base + c * p.ED * N) = make_float4(hlo.x, hlo.y, hhi.x, hhi.y);
         }
-        const float2 o = op[t * kTE + ((t & 1) ? op_off1 : op_off0)];   // {delta, delta*x}
-        const float4 Bq = *reinterpret_cast<const float4*>(sB + t * N);
-        const float4 Cq = *reinterpret_cast<const float4*>(sC + t * N);
+        const int r = rb0 + t * rstep;
+        const float2 o = op[r * kTE + ((t & 1) ? off_odd : off_even)];   // {delta, delta*x}
+        const float4 Bq = *reinterpret_cast<const float4*>(sB + r * N);
+        const float4 Cq = *reinterpret_cast<const float4*>(sC + r * N);
         const float2 dd = make_float2(o.x, o.x), dxx = make_float2(o.y, o.y);
         const float2 e_lo = __fmul2_rn(dd, A2lo), e_hi = __fmul2_rn(dd, A2hi);
         const float2 a_lo = make_float2(ex2f(e_lo.x), ex2f(e_lo.y));
@@ -176,7 +189,7 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
       const int r = int(kt % kStages);
       if (kt >= kStages && !mbar_wait(&raw_free[r], int((kt / kStages - 1) & 1))) return false;
       unsigned char* st = stage_ptr(kt);
-      const int t0 = int(kt * kTile);
+      const int t0 = int(tile_t0(kt));
       mbar_expect_tx(&raw_full[r], stage_tx);
       tma_load_3d(st, &maps.x, int(e0), t0, int(b), &raw_full[r]);
       tma_load_3d(st + S::kActBytes, &maps.d, int(e0), t0, int(b), &raw_full[r]);
@@ -188,7 +201,7 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
     // raw tile kt -> float32 operands in buffer kt & 1
     auto convert = [&](int64_t kt) {
       const int buf = int(kt & 1);
-      const int rows_ok = int(min64(kTile, p.L - kt * kTile));
+      const int rows_ok = int(min64(kTile, p.L - tile_t0(kt)));
       const unsigned char* st = stage_ptr(kt);
       const T* rx = reinterpret_cast<const T*>(st);
       const T* rd = reinterpret_cast<const T*>(st + S::kActBytes);
@@ -222,7 +235,7 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
     // finish tile kt: partial sums -> y (the consumers of tile kt have been waited for)
     auto epilogue = [&](int64_t kt) {
       const int buf = int(kt & 1);
-      const int64_t t0 = kt * kTile;
+      const int64_t t0 = tile_t0(kt);
       const int rows_ok = int(min64(kTile, p.L - t0));
       const unsigned char* st = stage_ptr(kt);
       const T* rx = reinterpret_cast<const T*>(st);
@@ -237,7 +250,8 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
         Vec4<T> out;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const float s = sum_lanes<kLPE>(yp + rr * kConsumers + yp_slot<kLPE, kTE>(rr, cc + k) * kLPE);
+          const int ps = rev ? kTile - 1 - rr : rr;          // processing step that produced row rr
+          const float s = sum_lanes<kLPE>(yp + ps * kConsumers + yp_slot<kLPE, kTE>(ps, cc + k) * kLPE);
           float yv = fmaf(s_D[cc + k], Elem<T>::to_f(xv.v[k]), s);
           if (has_z) {
             const float zf = Elem<T>::to_f(zv.v[k]);
@@ -291,7 +305,7 @@ int tma_launch_n(const SscanFwdParams& p, cudaStream_t st) {
   if (ok && p.z) ok = tma_encode(&m.z, p.z, bf, p.B, p.L, p.ED, p.z_sb, p.z_sl, G::kTE, kTile);
   else if (ok) m.z = m.x;
   if (!ok) return 1;                                   // caller falls back to the generic path
-  auto k = sscan_fwd_tma_kernel<T, N>;
+  auto k = (p.flags & MB200_REVERSE) ? sscan_fwd_tma_kernel<T, N, true> : sscan_fwd_tma_kernel<T, N, false>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess)
     return MB200_ELAUNCH;
   dim3 grid(unsigned((p.ED + G::kTE - 1) / G::kTE), unsigned(p.B));
@@ -376,6 +390,7 @@ extern "C" int mb200_sscan_fwd(const void* x, const void* delta, const void* z, 
     const int rc = dtype == MB200_F32 ? tma_launch_t<float>(p, N, st) : tma_launch_t<__nv_bfloat16>(p, N, st);
     if (rc <= 0) return rc;                        // launched (0) or failed hard (< 0)
   }
+  if (flags & MB200_REVERSE) return MB200_EUNSUPPORTED;   // the reverse direction exists on the tensor-map path only
   const int kv = dtype == MB200_F32 ? 4 : 8;
   bool vec = ED % kv == 0 && aligned16(x) && aligned16(delta) && aligned16(z) && aligned16(y) &&
              aligned16(Bm) && aligned16(Cm);

@@ -313,6 +313,7 @@ extern "C" const char* mb200_strerror(int code) {
     case MB200_ELAUNCH: return "CUDA kernel launch failed";
     case MB200_ETOOBIG: return "size exceeds a limit of this entry point";
     case MB200_ESETUP: return "per-device set-up failed";
+    case MB200_EUNSUPPORTED: return "option not available for these tensors";
     default: return "unknown error";
   }
 }

@@ -55,10 +55,12 @@ def _f32(t):
 
 
 def sscan_fwd_raw(x, delta, A, Bm, Cm, D, z=None, delta_bias=None, h0=None,
-                  want_last=False, want_carries=False, want_y=True):
+                  want_last=False, want_carries=False, want_y=True, reverse=False):
     """Launch the fused forward.  Tensors must already be prepared by the caller.
 
-    Returns (y, hT, carries); entries not asked for are None."""
+    Returns (y, hT, carries); entries not asked for are None.  With `reverse` the scan runs from the
+    last timestep to the first; None is returned when the kernels cannot do that for these tensors
+    (the caller then flips them itself)."""
     lib = _lib.load()
     Bsz, L, ED = x.shape
     N = A.shape[1]
@@ -68,7 +70,7 @@ def sscan_fwd_raw(x, delta, A, Bm, Cm, D, z=None, delta_bias=None, h0=None,
     chunk = lib.mb200_sscan_chunk()
     carries = (torch.empty((Bsz, (L + chunk - 1) // chunk, ED, N), dtype=torch.float32, device=dev)
                if want_carries else None)
-    flags = _lib.DELTA_SOFTPLUS if delta_bias is not None else 0
+    flags = (_lib.DELTA_SOFTPLUS if delta_bias is not None else 0) | (_lib.REVERSE if reverse else 0)
     zs = (z.stride(0), z.stride(1)) if z is not None else (0, 0)
     ys = (y.stride(0), y.stride(1)) if y is not None else (0, 0)
     with torch.cuda.device(dev):
@@ -79,12 +81,17 @@ def sscan_fwd_raw(x, delta, A, Bm, Cm, D, z=None, delta_bias=None, h0=None,
             x.stride(0), x.stride(1), delta.stride(0), delta.stride(1), zs[0], zs[1],
             Bm.stride(0), Bm.stride(1), Cm.stride(0), Cm.stride(1), ys[0], ys[1],
             _lib.dtype_code(x.dtype), flags, _lib.current_stream(dev))
+    if reverse and rc == _lib.EUNSUPPORTED:
+        return None
     _lib.check(rc, "mb200_sscan_fwd")
     return y, hT, carries
 
 
-def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None, want_g_out=False):
-    """Launch the fused backward.  Returns (dx, ddelta, dz, dB, dC, dA, dD, dbias, g_out)."""
+def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None, want_g_out=False,
+                  reverse=False):
+    """Launch the fused backward.  Returns (dx, ddelta, dz, dB, dC, dA, dD, dbias, g_out).
+
+    `reverse` must be what the forward that produced `carries` ran with."""
     lib = _lib.load()
     Bsz, L, ED = x.shape
     N = A.shape[1]
@@ -101,7 +108,7 @@ def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None,
     dD = acc[2 * nBC + nA:2 * nBC + nA + ED]
     dbias = acc[2 * nBC + nA + ED:] if delta_bias is not None else None
     g_out = torch.empty((Bsz, ED, N), dtype=torch.float32, device=dev) if want_g_out else None
-    flags = _lib.DELTA_SOFTPLUS if delta_bias is not None else 0
+    flags = (_lib.DELTA_SOFTPLUS if delta_bias is not None else 0) | (_lib.REVERSE if reverse else 0)
     zs = (z.stride(0), z.stride(1)) if z is not None else (0, 0)
     dzs = (dz.stride(0), dz.stride(1)) if dz is not None else (0, 0)
     with torch.cuda.device(dev):
@@ -122,7 +129,7 @@ class SelectiveScanFn(torch.autograd.Function):
     """y (and optionally the last state) of the fused scan; gradients for every input."""
 
     @staticmethod
-    def forward(ctx, x, delta, A, Bm, Cm, D, z, delta_bias, h0, return_last_state):
+    def forward(ctx, x, delta, A, Bm, Cm, D, z, delta_bias, h0, return_last_state, reverse=False):
         _require_cuda(x, delta, A, Bm, Cm, D, z, delta_bias, h0)
         dt = _act_dtype(x, delta, z, Bm, Cm)
         xs, ds, zs = _rows(x, dt), _rows(delta, dt), _rows(z, dt)
@@ -130,8 +137,22 @@ class SelectiveScanFn(torch.autograd.Function):
         A32, D32, b32, h032 = _f32(A), _f32(D), _f32(delta_bias), _f32(h0)
         needs_grad = any(t is not None and t.requires_grad
                          for t in (x, delta, A, Bm, Cm, D, z, delta_bias, h0))
-        y, hT, carries = sscan_fwd_raw(xs, ds, A32, Bs, Cs, D32, zs, b32, h032,
-                                       want_last=return_last_state, want_carries=needs_grad)
+        out = None
+        ctx.flipped = False
+        if reverse and not (needs_grad and A32.shape[1] != 16):    # the reverse backward exists for d_state 16
+            out = sscan_fwd_raw(xs, ds, A32, Bs, Cs, D32, zs, b32, h032, want_last=return_last_state,
+                                want_carries=needs_grad, reverse=True)
+        if reverse and out is None:
+            # what the reference does (mambapy/vim.py:228-261): scan the flipped sequence, flip back
+            xs, ds, zs, Bs, Cs = (None if t is None else t.flip(1) for t in (xs, ds, zs, Bs, Cs))
+            ctx.flipped = True
+        if out is None:
+            out = sscan_fwd_raw(xs, ds, A32, Bs, Cs, D32, zs, b32, h032,
+                                want_last=return_last_state, want_carries=needs_grad)
+        y, hT, carries = out
+        if ctx.flipped:
+            y = y.flip(1)
+        ctx.reverse = reverse and not ctx.flipped
         ctx.save_for_backward(xs, ds, A32, Bs, Cs, D32, zs, b32, carries)
         ctx.in_dtypes = tuple(None if t is None else t.dtype
                               for t in (x, delta, A, Bm, Cm, D, z, delta_bias, h0))
@@ -144,17 +165,19 @@ class SelectiveScanFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy, *unused):
         xs, ds, A32, Bs, Cs, D32, zs, b32, carries = ctx.saved_tensors
-        dy = _rows(dy, xs.dtype)
+        dy = _rows(dy.flip(1) if ctx.flipped else dy, xs.dtype)
         dx, dd, dz, dB, dC, dA, dD, dbias, g_out = sscan_bwd_raw(
-            xs, ds, A32, Bs, Cs, D32, zs, b32, dy, carries, want_g_out=ctx.has_h0)
+            xs, ds, A32, Bs, Cs, D32, zs, b32, dy, carries, want_g_out=ctx.has_h0, reverse=ctx.reverse)
+        if ctx.flipped:
+            dx, dd, dz, dB, dC = (None if t is None else t.flip(1) for t in (dx, dd, dz, dB, dC))
         tx, td, tA, tB, tC, tD, tz, tb, th = ctx.in_dtypes
         cast = lambda g, t: None if (g is None or t is None) else g.to(t)
         return (cast(dx, tx), cast(dd, td), cast(dA, tA), cast(dB, tB), cast(dC, tC),
-                cast(dD, tD), cast(dz, tz), cast(dbias, tb), cast(g_out, th), None)
+                cast(dD, tD), cast(dz, tz), cast(dbias, tb), cast(g_out, th), None, None)
 
 
 def selective_scan_fn(x, delta, A, B, C, D=None, z=None, delta_bias=None, h0=None,
-                      return_last_state=False):
+                      return_last_state=False, reverse=False):
     """Fused selective scan.
 
     x, delta, z : (B, L, ED)   B, C : (B, L, N)   A : (ED, N)   D : (ED)
@@ -162,8 +185,14 @@ def selective_scan_fn(x, delta, A, B, C, D=None, z=None, delta_bias=None, h0=Non
     contract of the fused seam at mambapy/mamba.py:260); with `z` it also applies the
     y * silu(z) gate (mambapy/mamba.py:229-231).  Returns y (B, L, ED), plus the final state
     (B, ED, N) float32 when `return_last_state`.
+
+    `reverse=True` scans from the last timestep to the first (h0 enters at t = L-1, the returned state
+    leaves t = 0): the second direction of the reference's bidirectional model, which flips the
+    sequence, scans and flips back (mambapy/vim.py:228-261).  The kernels do it in place when the
+    tensors meet the tensor-map alignment rules (and d_state is 16 if gradients are needed);
+    otherwise this function flips, as the reference does.
     """
-    return SelectiveScanFn.apply(x, delta, A, B, C, D, z, delta_bias, h0, return_last_state)
+    return SelectiveScanFn.apply(x, delta, A, B, C, D, z, delta_bias, h0, return_last_state, reverse)
 
 
 # ----------------------------------------------------------------- MambaBlock method drop-ins

@@ -149,6 +149,7 @@ class LayerParams(torch.nn.Module):
             self.out_proj.weight.copy_(u((d_model, ED), 1 / math.sqrt(ED)))
         self.A_log = nn.Parameter(torch.log(torch.arange(1, N + 1, dtype=torch.float32, device=device)).repeat(ED, 1))
         self.D = nn.Parameter(torch.ones(ED, device=device))
+        self.norm_weight = nn.Parameter(torch.ones(d_model, device=device))     # RMSNorm in front of the block
 
     def _apply_layernorms(self, dt, B, C):
         return dt, B, C
