@@ -66,6 +66,30 @@ __device__ __forceinline__ float softplus_fast(float x) {
   return e < 1e-2f ? e * (1.f - e * (0.5f - e * (1.f / 3.f))) : __logf(1.f + e);
 }
 
+// Two-lane versions of softplus_fast and x*sigmoid_fast(x) on the packed f32x2 instructions (the MUFU
+// calls stay scalar): the per-element warps of the fused kernels are bound by instruction issue.
+__device__ __forceinline__ float2 softplus_fast2(float2 x) {
+  const float2 m = __fmul2_rn(x, make_float2(1.4426950408889634f, 1.4426950408889634f));
+  const float2 e = make_float2(ex2f(m.x), ex2f(m.y));
+  // e*(1 - e*(1/2 - e/3)) where 1 + e would lose the small term, log(1 + e) elsewhere
+  const float2 third = make_float2(-1.f / 3.f, -1.f / 3.f), half = make_float2(0.5f, 0.5f), one = make_float2(1.f, 1.f);
+  const float2 nh = make_float2(-1.f, -1.f);
+  const float2 inner = __ffma2_rn(e, third, half);                       // 1/2 - e/3
+  const float2 poly = __fmul2_rn(e, __ffma2_rn(__fmul2_rn(e, inner), nh, one));
+  const float2 s = __fadd2_rn(e, one);
+  const float ln2 = 0.6931471805599453f;
+  const float2 lg = make_float2(__log2f(s.x) * ln2, __log2f(s.y) * ln2);
+  float2 r;
+  r.x = x.x > 20.f ? x.x : (e.x < 1e-2f ? poly.x : lg.x);
+  r.y = x.y > 20.f ? x.y : (e.y < 1e-2f ? poly.y : lg.y);
+  return r;
+}
+__device__ __forceinline__ float2 sigmoid_fast2(float2 x) {
+  const float2 m = __fmul2_rn(x, make_float2(-1.4426950408889634f, -1.4426950408889634f));
+  const float2 d = __fadd2_rn(make_float2(ex2f(m.x), ex2f(m.y)), make_float2(1.f, 1.f));
+  return make_float2(__fdividef(1.f, d.x), __fdividef(1.f, d.y));
+}
+
 // ---- packed float2 arithmetic (one issue slot for two lanes of FMA work) ------------
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
   float2 d;

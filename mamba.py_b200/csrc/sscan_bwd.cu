@@ -322,6 +322,8 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
       const T* rdy = reinterpret_cast<const T*>(st + 3 * S::kActBytes);
       float2* tile = s_op + buf * kBTile * kBTE;
       float* dyt = s_dyp + buf * kBTile * kBTE;
+      const float4 bq = *reinterpret_cast<const float4*>(s_bias + (lane & 7) * 4);   // this lane's 4 channels
+      const float bias4[4] = {bq.x, bq.y, bq.z, bq.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int v = lane + 32 * i;
@@ -334,17 +336,20 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
         float2 o[4];
         float dyo[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          float dv = Elem<T>::to_f(dv4.v[k]);
-          if (softplus) dv = softplus_fast(dv + s_bias[cc + k]);
-          if (rr >= rows_ok) dv = 0.f;
-          o[k] = make_float2(dv, dv * Elem<T>::to_f(xv.v[k]));
-          float g = Elem<T>::to_f(yv4.v[k]);
+        for (int k = 0; k < 4; k += 2) {                   // two channels at a time (packed arithmetic)
+          float2 dv = make_float2(Elem<T>::to_f(dv4.v[k]), Elem<T>::to_f(dv4.v[k + 1]));
+          if (softplus) dv = softplus_fast2(__fadd2_rn(dv, make_float2(bias4[k], bias4[k + 1])));
+          if (rr >= rows_ok) dv = make_float2(0.f, 0.f);
+          const float2 dx2 = __fmul2_rn(dv, make_float2(Elem<T>::to_f(xv.v[k]), Elem<T>::to_f(xv.v[k + 1])));
+          o[k] = make_float2(dv.x, dx2.x);
+          o[k + 1] = make_float2(dv.y, dx2.y);
+          float2 g = make_float2(Elem<T>::to_f(yv4.v[k]), Elem<T>::to_f(yv4.v[k + 1]));
           if (has_z) {
-            const float zf = Elem<T>::to_f(zv4.v[k]);
-            g *= zf * sigmoid_fast(zf);
+            const float2 zf = make_float2(Elem<T>::to_f(zv4.v[k]), Elem<T>::to_f(zv4.v[k + 1]));
+            g = __fmul2_rn(g, __fmul2_rn(zf, sigmoid_fast2(zf)));
           }
-          dyo[k] = g;
+          dyo[k] = g.x;
+          dyo[k + 1] = g.y;
         }
         *reinterpret_cast<float4*>(tile + op_index(rr, cc, kBTE)) = make_float4(o[0].x, o[0].y, o[1].x, o[1].y);
         *reinterpret_cast<float4*>(tile + op_index(rr, cc + 2, kBTE)) = make_float4(o[2].x, o[2].y, o[3].x, o[3].y);
