@@ -11,20 +11,16 @@ import torch
 import torch.nn.functional as F
 
 from . import workloads
-from .mamba import ssm_step_fn, conv_step_fn, sscan_fwd_raw, sscan_bwd_raw
+from .mamba import ssm_step_fn, conv_step_fn, sscan_fwd_raw, sscan_bwd_raw, rms_norm
 
 
 # ----------------------------------------------------------------------------------- decode
-def _rms(x, w, eps=1e-5):
-    return (x * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + eps).to(x.dtype)) * w
-
-
 def decode_layer_step(W, x, h, win):
     """One ResidualBlock.step (mambapy/mamba.py:114-125, :351-382) on explicit weights, with the
     caches updated in place.  x: (B, D); h: (B, ED, N) f32; win: (B, ED, d_conv-1)."""
     R = W["dt_w"].shape[1]
     N = W["A"].shape[1]
-    xz = F.linear(_rms(x, W["norm_w"]), W["in_proj"])
+    xz = F.linear(rms_norm(x, W["norm_w"], 1e-5), W["in_proj"])
     xs, z = xz.chunk(2, dim=1)
     xc, _ = conv_step_fn(xs, win, W["conv_w"], W["conv_b"], inplace=True)
     dbc = F.linear(xc, W["x_proj"])

@@ -107,7 +107,7 @@ def decode_layer_weights(seed: int, device, d_model=2560, N=16, d_conv=4, dtype=
     ED, R = 2 * d_model, math.ceil(d_model / 16)
     u = lambda shape, bound: ((torch.rand(shape, generator=gen, device=device) * 2 - 1) * bound)
     return dict(
-        norm_w=torch.ones(d_model, device=device, dtype=dtype),
+        norm_w=torch.ones(d_model, device=device),             # RMSNorm gain, float32 like the kernel takes it
         in_proj=u((2 * ED, d_model), 1 / math.sqrt(d_model)).to(dtype),
         conv_w=u((ED, 1, d_conv), 1 / math.sqrt(d_conv)),      # the kernel takes the filter in float32
         conv_b=u((ED,), 1 / math.sqrt(d_conv)),
