@@ -383,7 +383,7 @@ def bench_scan_130m(args, rank, world, dev):
     for _ in range(3):
         e2e_step()
     e2e_finish()
-    k_e2e = max(4, min(args.steps, 12))
+    k_e2e = max(8, min(args.steps, 12))          # enough steps for the two-slot pipeline to reach its steady state
     ems, _, _ = time_region(e2e_step, k_e2e, world, finish=e2e_finish)
     sampler.stop()
     host_out = slots[0]["host"]
