@@ -106,6 +106,10 @@ struct SscanBwdParams {
 
 }  // namespace mb200
 
+// Internal flag (never part of the public flags): run the forward kernel as the reverse carry pass.
+namespace mb200 { constexpr int kFlagCarryPass = 1 << 16; }
+int mb200_fwd_tma_try(const mb200::SscanFwdParams& p, int N, int dtype, cudaStream_t st);
+
 // Device-side status words of the kernels that contain bounded waits (host functions; each reads
 // and clears its kernel's word, synchronising the device).
 int mb200_fwd_device_status();

@@ -164,6 +164,18 @@ extern "C" int mb200_sscan_bwd_carry(const void* delta, const void* z, const voi
   p.B = B; p.L = L; p.ED = ED;
   p.d_sb = d_sb; p.d_sl = d_sl; p.z_sb = z_sb; p.z_sl = z_sl; p.dy_sb = dy_sb; p.dy_sl = dy_sl;
   p.c_sb = c_sb; p.c_sl = c_sl; p.flags = flags;
+  {
+    // tensor-map path: the forward kernel in its carry mode (dy in the place of x, C in the place of B)
+    SscanFwdParams f;
+    f.x = dy; f.delta = delta; f.z = z; f.Bm = Cm; f.Cm = Cm; f.A = A; f.D = nullptr;
+    f.delta_bias = delta_bias; f.h0 = nullptr; f.y = nullptr; f.hT = g_out; f.carries = nullptr;
+    f.B = B; f.L = L; f.ED = ED;
+    f.x_sb = dy_sb; f.x_sl = dy_sl; f.d_sb = d_sb; f.d_sl = d_sl; f.z_sb = z_sb; f.z_sl = z_sl;
+    f.b_sb = c_sb; f.b_sl = c_sl; f.c_sb = c_sb; f.c_sl = c_sl; f.y_sb = 0; f.y_sl = 0;
+    f.flags = (flags & MB200_DELTA_SOFTPLUS) | MB200_REVERSE | kFlagCarryPass;
+    const int rc = mb200_fwd_tma_try(f, N, dtype, st);
+    if (rc <= 0) return rc;                                  // launched, or failed hard
+  }
   const int kv = dtype == MB200_F32 ? 4 : 8;
   bool vec = ED % kv == 0 && aligned16(delta) && aligned16(z) && aligned16(dy) && aligned16(Cm);
   for (int64_t s : {d_sb, d_sl, dy_sb, dy_sl, c_sb, c_sl}) vec = vec && s % kv == 0;

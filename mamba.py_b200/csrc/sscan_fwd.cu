@@ -61,7 +61,11 @@ template <typename T, int N> struct TmaFwdSmem {
   static constexpr int kBytes = kBars + (2 * kStages + 4) * 8;
 };
 
-template <typename T, int N, bool kRev>
+// kCarry turns the kernel into the reverse carry pass of the sequence-sharded backward
+// (gc <- a[t] * (dy'[t] * C[t] + gc), t = L-1 ... 0): the caller passes dy as `x` and C as `Bm`, the
+// converter forms dy' = dy * silu(z) instead of delta * x, and the recurrence multiplies by the decay
+// after adding the input.  It has no y and saves no states; the result leaves through hT.
+template <typename T, int N, bool kRev, bool kCarry = false>
 __global__ void __launch_bounds__(kTmaThreads, 3)
 sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams p) {
   using G = SscanGeom<N>;
@@ -156,18 +160,24 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
         const int r = rb0 + t * rstep;
         const float2 o = op[r * kTE + ((t & 1) ? off_odd : off_even)];   // {delta, delta*x}
         const float4 Bq = *reinterpret_cast<const float4*>(sB + r * N);
-        const float4 Cq = *reinterpret_cast<const float4*>(sC + r * N);
+        float4 Cq = Bq;
+        if constexpr (!kCarry) Cq = *reinterpret_cast<const float4*>(sC + r * N);
         const float2 dd = make_float2(o.x, o.x), dxx = make_float2(o.y, o.y);
         const float2 e_lo = __fmul2_rn(dd, A2lo), e_hi = __fmul2_rn(dd, A2hi);
         const float2 a_lo = make_float2(ex2f(e_lo.x), ex2f(e_lo.y));
         const float2 a_hi = make_float2(ex2f(e_hi.x), ex2f(e_hi.y));
-        const float2 u_lo = __fmul2_rn(dxx, make_float2(Bq.x, Bq.y));
-        const float2 u_hi = __fmul2_rn(dxx, make_float2(Bq.z, Bq.w));
-        hlo = __ffma2_rn(a_lo, hlo, u_lo);
-        hhi = __ffma2_rn(a_hi, hhi, u_hi);
-        float2 acc = __fmul2_rn(hlo, make_float2(Cq.x, Cq.y));
-        acc = __ffma2_rn(hhi, make_float2(Cq.z, Cq.w), acc);
-        if (has_y) yp[t * kConsumers + ((t & 1) ? yp_off1 : yp_off0)] = acc.x + acc.y;
+        if constexpr (kCarry) {
+          hlo = __fmul2_rn(a_lo, __ffma2_rn(dxx, make_float2(Bq.x, Bq.y), hlo));
+          hhi = __fmul2_rn(a_hi, __ffma2_rn(dxx, make_float2(Bq.z, Bq.w), hhi));
+        } else {
+          const float2 u_lo = __fmul2_rn(dxx, make_float2(Bq.x, Bq.y));
+          const float2 u_hi = __fmul2_rn(dxx, make_float2(Bq.z, Bq.w));
+          hlo = __ffma2_rn(a_lo, hlo, u_lo);
+          hhi = __ffma2_rn(a_hi, hhi, u_hi);
+          float2 acc = __fmul2_rn(hlo, make_float2(Cq.x, Cq.y));
+          acc = __ffma2_rn(hhi, make_float2(Cq.z, Cq.w), acc);
+          if (has_y) yp[t * kConsumers + ((t & 1) ? yp_off1 : yp_off0)] = acc.x + acc.y;
+        }
       }
       mbar_arrive(&op_empty[buf]);
     }
@@ -210,13 +220,26 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
         const int rr = v / kVecPerRow, cc = (v % kVecPerRow) * 4;
         const Vec4<T> xv = *reinterpret_cast<const Vec4<T>*>(rx + rr * kTE + cc);
         const Vec4<T> dv4 = *reinterpret_cast<const Vec4<T>*>(rd + rr * kTE + cc);
+        Vec4<T> zv4 = xv;
+        if constexpr (kCarry) {
+          if (has_z) zv4 = *reinterpret_cast<const Vec4<T>*>(reinterpret_cast<const T*>(st + 2 * S::kActBytes) + rr * kTE + cc);
+        }
         float2 o[4];
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           float dv = Elem<T>::to_f(dv4.v[k]);
           if (softplus) dv = softplus_fast(dv + s_bias[cc + k]);
           if (rr >= rows_ok) dv = 0.f;                      // past the end of the sequence
-          o[k] = make_float2(dv, dv * Elem<T>::to_f(xv.v[k]));
+          if constexpr (kCarry) {
+            float g = Elem<T>::to_f(xv.v[k]);               // dy in the place of x
+            if (has_z) {
+              const float zf = Elem<T>::to_f(zv4.v[k]);
+              g *= zf * sigmoid_fast(zf);
+            }
+            o[k] = make_float2(dv, g);
+          } else {
+            o[k] = make_float2(dv, dv * Elem<T>::to_f(xv.v[k]));
+          }
         }
         *reinterpret_cast<float4*>(tile + op_index(rr, cc, kTE)) = make_float4(o[0].x, o[0].y, o[1].x, o[1].y);
         *reinterpret_cast<float4*>(tile + op_index(rr, cc + 2, kTE)) = make_float4(o[2].x, o[2].y, o[3].x, o[3].y);
@@ -305,7 +328,8 @@ int tma_launch_n(const SscanFwdParams& p, cudaStream_t st) {
   if (ok && p.z) ok = tma_encode(&m.z, p.z, bf, p.B, p.L, p.ED, p.z_sb, p.z_sl, G::kTE, kTile);
   else if (ok) m.z = m.x;
   if (!ok) return 1;                                   // caller falls back to the generic path
-  auto k = (p.flags & MB200_REVERSE) ? sscan_fwd_tma_kernel<T, N, true> : sscan_fwd_tma_kernel<T, N, false>;
+  auto k = (p.flags & kFlagCarryPass) ? sscan_fwd_tma_kernel<T, N, true, true>
+           : (p.flags & MB200_REVERSE) ? sscan_fwd_tma_kernel<T, N, true> : sscan_fwd_tma_kernel<T, N, false>;
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess)
     return MB200_ELAUNCH;
   dim3 grid(unsigned((p.ED + G::kTE - 1) / G::kTE), unsigned(p.B));
@@ -343,6 +367,14 @@ bool tma_path_ok(const SscanFwdParams& p, int N, int es) {
 using namespace mb200;
 
 extern "C" int mb200_sscan_chunk(void) { return kChunk; }
+
+// Internal: the tensor-map forward on a prepared parameter block (used by the reverse carry pass).
+// Returns 0 when launched, a negative code on failure, 1 when these tensors need the generic path.
+int mb200_fwd_tma_try(const mb200::SscanFwdParams& p, int N, int dtype, cudaStream_t st) {
+  const int es = dtype == MB200_F32 ? 4 : 2;
+  if (!tma_path_ok(p, N, es)) return 1;
+  return dtype == MB200_F32 ? tma_launch_t<float>(p, N, st) : tma_launch_t<__nv_bfloat16>(p, N, st);
+}
 
 // Reads (and clears) the device-side status word of the forward kernels: non-zero when a bounded
 // wait inside a kernel gave up.  Synchronises the device.
