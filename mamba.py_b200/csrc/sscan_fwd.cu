@@ -65,7 +65,8 @@ template <typename T, int N> struct TmaFwdSmem {
 // (gc <- a[t] * (dy'[t] * C[t] + gc), t = L-1 ... 0): the caller passes dy as `x` and C as `Bm`, the
 // converter forms dy' = dy * silu(z) instead of delta * x, and the recurrence multiplies by the decay
 // after adding the input.  It has no y and saves no states; the result leaves through hT.
-template <typename T, int N, bool kRev, bool kCarry = false>
+// kHasY = false is the pass that only wants states (no C-contraction, no epilogue).
+template <typename T, int N, bool kRev, bool kCarry, bool kHasY>
 __global__ void __launch_bounds__(kTmaThreads, 3)
 sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams p) {
   using G = SscanGeom<N>;
@@ -90,7 +91,7 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
   const int64_t b = blockIdx.y;
   const int cols_ok = int(min64(kTE, p.ED - e0));
   const bool softplus = (p.flags & MB200_DELTA_SOFTPLUS) != 0;
-  const bool has_y = p.y != nullptr;
+  constexpr bool has_y = kHasY;
   const bool has_z = p.z != nullptr;
   const int64_t ntiles = (p.L + kTile - 1) / kTile;
   // Direction.  With MB200_REVERSE time is walked from L-1 down to 0: processing tile kt is the
@@ -161,7 +162,7 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
         const float2 o = op[r * kTE + ((t & 1) ? off_odd : off_even)];   // {delta, delta*x}
         const float4 Bq = *reinterpret_cast<const float4*>(sB + r * N);
         float4 Cq = Bq;
-        if constexpr (!kCarry) Cq = *reinterpret_cast<const float4*>(sC + r * N);
+        if constexpr (kHasY) Cq = *reinterpret_cast<const float4*>(sC + r * N);
         const float2 dd = make_float2(o.x, o.x), dxx = make_float2(o.y, o.y);
         const float2 e_lo = __fmul2_rn(dd, A2lo), e_hi = __fmul2_rn(dd, A2hi);
         const float2 a_lo = make_float2(ex2f(e_lo.x), ex2f(e_lo.y));
@@ -174,9 +175,11 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
           const float2 u_hi = __fmul2_rn(dxx, make_float2(Bq.z, Bq.w));
           hlo = __ffma2_rn(a_lo, hlo, u_lo);
           hhi = __ffma2_rn(a_hi, hhi, u_hi);
-          float2 acc = __fmul2_rn(hlo, make_float2(Cq.x, Cq.y));
-          acc = __ffma2_rn(hhi, make_float2(Cq.z, Cq.w), acc);
-          if (has_y) yp[t * kConsumers + ((t & 1) ? yp_off1 : yp_off0)] = acc.x + acc.y;
+          if constexpr (kHasY) {
+            float2 acc = __fmul2_rn(hlo, make_float2(Cq.x, Cq.y));
+            acc = __ffma2_rn(hhi, make_float2(Cq.z, Cq.w), acc);
+            yp[t * kConsumers + ((t & 1) ? yp_off1 : yp_off0)] = acc.x + acc.y;
+          }
         }
       }
       mbar_arrive(&op_empty[buf]);
@@ -328,8 +331,10 @@ int tma_launch_n(const SscanFwdParams& p, cudaStream_t st) {
   if (ok && p.z) ok = tma_encode(&m.z, p.z, bf, p.B, p.L, p.ED, p.z_sb, p.z_sl, G::kTE, kTile);
   else if (ok) m.z = m.x;
   if (!ok) return 1;                                   // caller falls back to the generic path
-  auto k = (p.flags & kFlagCarryPass) ? sscan_fwd_tma_kernel<T, N, true, true>
-           : (p.flags & MB200_REVERSE) ? sscan_fwd_tma_kernel<T, N, true> : sscan_fwd_tma_kernel<T, N, false>;
+  const bool rv = (p.flags & MB200_REVERSE) != 0, hy = p.y != nullptr;
+  auto k = (p.flags & kFlagCarryPass) ? sscan_fwd_tma_kernel<T, N, true, true, false>
+           : rv ? (hy ? sscan_fwd_tma_kernel<T, N, true, false, true> : sscan_fwd_tma_kernel<T, N, true, false, false>)
+                : (hy ? sscan_fwd_tma_kernel<T, N, false, false, true> : sscan_fwd_tma_kernel<T, N, false, false, false>);
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess)
     return MB200_ELAUNCH;
   dim3 grid(unsigned((p.ED + G::kTE - 1) / G::kTE), unsigned(p.B));
