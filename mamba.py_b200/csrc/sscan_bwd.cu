@@ -78,7 +78,9 @@ __device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
   asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
 }
 
-template <typename T, bool kRev>
+// The softplus option and the presence of the gate are template parameters too: as run-time flags they
+// cost the converter and finishing warps (the busiest ones) branches and selects, 6 % of the launch.
+template <typename T, bool kRev, bool kSoftplus, bool kHasZ>
 __global__ void __launch_bounds__(kBwdThreads, 3)
 sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams p) {
   using S = TmaBwdSmem<T>;
@@ -106,8 +108,8 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
   const int64_t e0 = int64_t(blockIdx.x) * kBTE;
   const int64_t b = blockIdx.y;
   const int cols_ok = int(min64(kBTE, p.ED - e0));
-  const bool softplus = (p.flags & MB200_DELTA_SOFTPLUS) != 0;
-  const bool has_z = p.z != nullptr;
+  constexpr bool softplus = kSoftplus;
+  constexpr bool has_z = kHasZ;
   const int64_t ntiles = (p.L + kBTile - 1) / kBTile;
   // Direction of the scan being differentiated (MB200_REVERSE: it ran from t = L-1 down to 0).  Tiles
   // are taken in the opposite order of that scan: iteration j works on the tile that starts at
@@ -516,7 +518,14 @@ int bwd_tma_launch(const SscanBwdParams& p, cudaStream_t st) {
   if (ok && p.z) ok = tma_encode(&m.z, p.z, bf, p.B, p.L, p.ED, p.z_sb, p.z_sl, kBTE, kBTile);
   else if (ok) m.z = m.x;
   if (!ok) return 1;                                   // caller falls back to the generic path
-  auto k = (p.flags & MB200_REVERSE) ? sscan_bwd_tma_kernel<T, true> : sscan_bwd_tma_kernel<T, false>;
+  const bool rv = (p.flags & MB200_REVERSE) != 0, sp = (p.flags & MB200_DELTA_SOFTPLUS) != 0, hz = p.z != nullptr;
+  void (*k)(const BwdMaps, const SscanBwdParams) = nullptr;
+#define MB200_BWD_PICK(R, S, Z) if (rv == R && sp == S && hz == Z) k = sscan_bwd_tma_kernel<T, R, S, Z>;
+  MB200_BWD_PICK(false, false, false) MB200_BWD_PICK(false, false, true)
+  MB200_BWD_PICK(false, true, false) MB200_BWD_PICK(false, true, true)
+  MB200_BWD_PICK(true, false, false) MB200_BWD_PICK(true, false, true)
+  MB200_BWD_PICK(true, true, false) MB200_BWD_PICK(true, true, true)
+#undef MB200_BWD_PICK
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess)
     return MB200_ELAUNCH;
   dim3 grid(unsigned((p.ED + kBTE - 1) / kBTE), unsigned(p.B));
