@@ -324,13 +324,13 @@ def bench_scan_130m(args, rank, world, dev):
     }
     res["dominant"] = ("sscan_bwd_kernel", bwd_bytes, bwd_ms)
     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of that kernel on this exact workload,
-    # from the ncu capture summarised in profiles/sscan_bwd_kernel__scan_130m.md (406.6 MB + 132.9 MB;
+    # from the ncu capture summarised in profiles/sscan_bwd_kernel__scan_130m.md (406.6 MB + 132.0 MB;
     # 354.4 MB algorithmic plus 201 MB of saved scan states read back)
-    res["traffic"] = 539.5e6
+    res["traffic"] = 538.6e6
     # why the HBM fraction is small: what the same capture shows to be busy instead (static figures of
     # that capture, not re-measured here)
     res["roofline_note"] = ("the fused backward is not HBM-bound: ncu shows DRAM at 9 % of peak while the "
-                            "shared-memory pipe is at 69 %, instruction issue at 59 %, FMA 39 %, MUFU 32 % "
+                            "shared-memory pipe is at 72 %, instruction issue at 60 %, FMA 41 %, MUFU 33 % "
                             "(profiles/sscan_bwd_kernel__scan_130m.md)")
 
     if args.skip_e2e:
