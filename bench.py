@@ -3,17 +3,27 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
-Workloads (a "step" is one forward+backward pass of the scan over one synthetic batch):
-  scan_130m  (default) fused selective scan fwd+bwd on the Mamba-130m layer shape
-             (B=8 per GPU, L=2048, ED=1536, N=16, bf16 I/O, float32 state).  With N GPUs every
-             rank scans its own batch (the path shards over batch with no communication).
-  pscan      the PScan operator fwd+bwd, float32, (16, 2048, 1536, 16) per GPU.
-  decode     one Mamba-2.8b-shaped layer-step (B=256, ED=5120) repeated; state traffic bound.
-  lshard     the long sequence (1, 131072, 5120, 16) bf16 split over the N GPUs along L, with
-             the carry all-gather between the local scans (strong scaling).
+A "step" is one forward+backward pass of the scan over one synthetic batch.  The headline (`value`,
+`ms_per_step`, `roofline`, `e2e`) is always the fused selective scan on the Mamba-130m layer shape
+(B=8 per GPU, L=2048, ED=1536, N=16, bf16 I/O, float32 state, softplus(delta+bias) and gate inside);
+with N GPUs every rank scans its own batch (the path shards over batch with no communication).
+The timed region of K steps is repeated `--regions` times; `ms_per_step` is the median region.
 
-`--impl reference` times the reference's own algorithm (the CPU restatement under oracle/,
-PyTorch ops on the host cores) on a bounded sample of the same workload.
+The default workload `all` adds, in the same line:
+  "lshard"   the long sequence (1, 131072, 5120, 16) bf16 split along L over the N GPUs (strong
+             scaling; N=1 runs it sub-sharded on one GPU), with the time of each pass and of the
+             collectives, preceded by a parity self-check of the sharded scan against the single
+             launch on a short sequence ("lshard_parity");
+  "pscan", "decode", "b1_long"   (N=1 only) the PScan operator (16, 2048, 1536, 16) float32, the
+             Mamba-2.8b-shaped 64-layer decode step (B=256), and the batch-1 shapes the reference
+             publishes, each with its dominant kernel's roofline fraction;
+  "reference_on_gpu"   (N=1 only) the reference's own parallel-scan path run with PyTorch on this
+             same GPU, as a second comparison (the contract baseline is the CPU arm).
+`--workload scan_130m|pscan|decode|lshard|layer` runs that one workload as the headline instead.
+
+`--impl reference` times the reference's own implementation on the host cores on a bounded sample
+of the headline workload: the unmodified reference from oracle/_ref when it has been made
+(kind "reference"), else the CPU restatement under oracle/ (kind "port").
 """
 from __future__ import annotations
 
@@ -133,6 +143,18 @@ def time_region(fn, steps, world, finish=None):
     return ms, t_lo, t_hi
 
 
+def time_regions(fn, steps, world, regions, finish=None):
+    """`regions` timed regions of exactly `steps` steps each.  Returns (median region ms, every
+    region's ms, host time of the first region's start, of the last region's end)."""
+    out, lo, hi = [], None, None
+    for _ in range(max(1, regions)):
+        ms, t_lo, t_hi = time_region(fn, steps, world, finish)
+        out.append(ms)
+        lo = t_lo if lo is None else lo
+        hi = t_hi
+    return statistics.median(out), out, lo, hi
+
+
 def time_kernel(fn, iters=10):
     """Average device time (ms) of one launch, each launch timed by its own event pair."""
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
@@ -146,61 +168,86 @@ def time_kernel(fn, iters=10):
     return sum(ts) / len(ts), min(ts)
 
 
+class Timing:
+    """What the GPU legs (bench_legs.py) get from this file: one definition of "timed region"."""
+    ClockSampler = ClockSampler
+    time_region = staticmethod(time_region)
+    time_regions = staticmethod(time_regions)
+    time_kernel = staticmethod(time_kernel)
+
+
 # ------------------------------------------------------------------------- CPU baseline
-def cpu_reference_scan_fwd_bwd(Bsz, L, ED, N, seed, threads):
-    """One fwd+bwd of the reference's selective_scan + gate (parallel-scan route) on the host."""
+def reference_functions():
+    """(kind, selective_scan(x, delta, A, B, C, D), pscan(A, X)) of the reference's own code: the
+    unmodified reference package from oracle/_ref when it has been made there ("reference"), else the
+    CPU restatement under oracle/ ("port").  Both run on whatever device their tensors are on."""
+    from oracle.make_ref import ref_path
+    p = ref_path()
+    if p is not None:
+        if p not in sys.path:
+            sys.path.insert(0, p)
+        import mambapy.mamba as rm
+        import mambapy.pscan as rp
+        return "reference", (lambda x, d, A, B, C, D: rm.MambaBlock.selective_scan(None, x, d, A, B, C, D)), rp.pscan
     from oracle import scan_oracle as O
+    return "port", O.selective_scan, O.pscan
+
+
+def reference_scan_fwd_bwd(Bsz, L, ED, N, seed, device="cpu"):
+    """One fwd+bwd of the reference's selective_scan + gate (mambapy/mamba.py:274-295, :229-231),
+    float32, on `device`.  Returns (step function, kind)."""
     import torch.nn.functional as F
-    torch.set_num_threads(threads)
+    kind, scan, _ = reference_functions()
     g = torch.Generator().manual_seed(seed)
-    x = torch.randn(Bsz, L, ED, generator=g).requires_grad_()
-    delta = F.softplus(torch.randn(Bsz, L, ED, generator=g) * 0.5 - 4.6).requires_grad_()
-    A = (-torch.arange(1, N + 1, dtype=torch.float32).repeat(ED, 1)).requires_grad_()
-    Bm = torch.randn(Bsz, L, N, generator=g).requires_grad_()
-    Cm = torch.randn(Bsz, L, N, generator=g).requires_grad_()
-    D = torch.ones(ED, requires_grad=True)
-    z = torch.randn(Bsz, L, ED, generator=g).requires_grad_()
-    gy = torch.randn(Bsz, L, ED, generator=g)
+    mk = lambda *s: torch.randn(*s, generator=g)
+    x = mk(Bsz, L, ED).to(device).requires_grad_()
+    delta = F.softplus(mk(Bsz, L, ED) * 0.5 - 4.6).to(device).requires_grad_()
+    A = (-torch.arange(1, N + 1, dtype=torch.float32).repeat(ED, 1)).to(device).requires_grad_()
+    Bm = mk(Bsz, L, N).to(device).requires_grad_()
+    Cm = mk(Bsz, L, N).to(device).requires_grad_()
+    D = torch.ones(ED, device=device, requires_grad=True)
+    z = mk(Bsz, L, ED).to(device).requires_grad_()
+    gy = mk(Bsz, L, ED).to(device)
 
     def step():
         for t in (x, delta, A, Bm, Cm, D, z):
             t.grad = None
-        y = O.gate(O.selective_scan(x, delta, A, Bm, Cm, D), z)
+        y = scan(x, delta, A, Bm, Cm, D) * F.silu(z)
         y.backward(gy)
-    return step
+    return step, kind
 
 
-def cpu_reference_pscan_fwd_bwd(Bsz, L, D, N, seed, threads):
-    from oracle import scan_oracle as O
+def reference_pscan_fwd_bwd(Bsz, L, D, N, seed, device="cpu"):
     import torch.nn.functional as F
-    torch.set_num_threads(threads)
+    kind, _, pscan = reference_functions()
     g = torch.Generator().manual_seed(seed)
-    A = torch.exp(-F.softplus(torch.randn(Bsz, L, D, N, generator=g))).requires_grad_()
-    X = torch.randn(Bsz, L, D, N, generator=g).requires_grad_()
-    G = torch.randn(Bsz, L, D, N, generator=g)
+    A = torch.exp(-F.softplus(torch.randn(Bsz, L, D, N, generator=g))).to(device).requires_grad_()
+    X = torch.randn(Bsz, L, D, N, generator=g).to(device).requires_grad_()
+    G = torch.randn(Bsz, L, D, N, generator=g).to(device)
 
     def step():
         A.grad = None
         X.grad = None
-        O.pscan(A, X).backward(G)
-    return step
+        pscan(A, X).backward(G)
+    return step, kind
 
 
 CPU_SAMPLES = {
     # workload: (builder, kwargs of the bounded sample, tokens in the sample, description)
-    "scan_130m": (cpu_reference_scan_fwd_bwd, dict(Bsz=1, L=2048, ED=1536, N=16), 2048,
+    "scan_130m": (reference_scan_fwd_bwd, dict(Bsz=1, L=2048, ED=1536, N=16), 2048,
                   "1 of the 8 batch rows (B=1, L=2048, ED=1536, N=16), float32, selective_scan+gate fwd+bwd"),
-    "lshard": (cpu_reference_scan_fwd_bwd, dict(Bsz=1, L=1024, ED=5120, N=16), 1024,
+    "lshard": (reference_scan_fwd_bwd, dict(Bsz=1, L=1024, ED=5120, N=16), 1024,
                "first 1024 of 131072 timesteps (B=1, ED=5120, N=16), float32, selective_scan+gate fwd+bwd"),
-    "pscan": (cpu_reference_pscan_fwd_bwd, dict(Bsz=1, L=2048, D=1536, N=16), 2048,
+    "pscan": (reference_pscan_fwd_bwd, dict(Bsz=1, L=2048, D=1536, N=16), 2048,
               "1 of the 16 batch rows (B=1, L=2048, D=1536, N=16), float32, pscan fwd+bwd"),
 }
 
 
 def cpu_baseline(workload, repeats=3):
     threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
     builder, kw, tokens, desc = CPU_SAMPLES[workload]
-    step = builder(seed=1002, threads=threads, **kw)
+    step, kind = builder(seed=1002, **kw)
     step()                                            # warm-up
     ts = []
     for _ in range(repeats):
@@ -208,17 +255,18 @@ def cpu_baseline(workload, repeats=3):
         step()
         ts.append(time.perf_counter() - t)
     return {"value": tokens / statistics.median(ts), "unit": "tokens/s", "cores": threads,
-            "kind": "port", "sample": desc, "s_per_sample": statistics.median(ts)}
+            "kind": kind, "sample": desc, "s_per_sample": statistics.median(ts)}
 
 
 def run_reference(args, rank):
-    """The reference arm: the reference's own CPU algorithm on the host cores, rank 0 only."""
+    """The reference arm: the reference's own CPU implementation on the host cores, rank 0 only."""
     if rank != 0:
         return
     wl = args.workload if args.workload in CPU_SAMPLES else "scan_130m"
     threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
     builder, kw, tokens, desc = CPU_SAMPLES[wl]
-    step = builder(seed=1002, threads=threads, **kw)
+    step, kind = builder(seed=1002, **kw)
     for _ in range(max(1, min(args.warmup, 2))):
         step()
     t0 = time.perf_counter()
@@ -231,7 +279,7 @@ def run_reference(args, rank):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": SCALING[wl], "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": workload_config(wl, args.gpus),
-        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": desc},
+        "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": kind, "sample": desc},
         "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -242,6 +290,7 @@ METRIC = {"scan_130m": "selective_scan_fwd_bwd_tokens_per_s", "lshard": "selecti
           "pscan": "pscan_fwd_bwd_tokens_per_s", "decode": "decode_layer_steps_tokens_per_s",
           "layer": "mamba_layer_fwd_bwd_tokens_per_s"}
 SCALING = {"scan_130m": "weak", "pscan": "weak", "decode": "weak", "lshard": "strong", "layer": "weak"}
+DTYPE = {"scan_130m": "bf16", "pscan": "f32", "decode": "bf16", "lshard": "bf16", "layer": "bf16"}
 
 
 def workload_config(wl, n):
@@ -255,10 +304,10 @@ def workload_config(wl, n):
                 "D": 1536, "N": 16, "io_dtype": "f32", "parallelism": f"batch-sharded x{n}, no collective",
                 "l2": "25.8 GB touched per step, larger than L2"}
     if wl == "decode":
-        return {"workload": "one Mamba-2.8b-shaped layer-step (conv window + SSM state update + gate)",
+        return {"workload": "Mamba-2.8b-shaped decode step, 64 layers (conv window + SSM state update + gate per layer)",
                 "B_per_gpu": 256, "global_batch": 256 * n, "ED": 5120, "N": 16, "io_dtype": "bf16",
                 "state_dtype": "f32", "parallelism": f"batch-sharded x{n}, no collective",
-                "l2": "8 layers' states (0.67 GB) are cycled so every step misses L2"}
+                "l2": "the 64 layers' states (5.4 GB) are walked in turn so every layer-step misses L2"}
     if wl == "layer":
         return {"workload": "one whole Mamba-130m-shaped residual layer fwd+bwd (projections by the GEMM library; RMSNorm, "
                             "conv1d+SiLU and gated scan by this library), bf16 autocast, float32 scan state",
@@ -271,201 +320,19 @@ def workload_config(wl, n):
             "l2": "14.8 GB touched per step, larger than L2"}
 
 
-# ------------------------------------------------------------------------- GPU workloads
-def bench_scan_130m(args, rank, world, dev):
-    import mamba_b200
-    from mamba_b200 import workloads
-    from mamba_b200.mamba import sscan_fwd_raw, sscan_bwd_raw
-    Bsz, L, ED, N = 8, 2048, 1536, 16
-    w = workloads.layer_130m_scan_inputs(1002 + rank, dev, Bsz=Bsz, L=L)
-    leaves = {k: w[k].clone().requires_grad_() for k in ("x", "delta_raw", "z", "B", "C", "A", "D", "delta_bias")}
-
-    def step():
-        for t in leaves.values():
-            t.grad = None
-        y = mamba_b200.selective_scan_fn(leaves["x"], leaves["delta_raw"], leaves["A"], leaves["B"], leaves["C"],
-                                         leaves["D"], z=leaves["z"], delta_bias=leaves["delta_bias"])
-        y.backward(w["dy"])
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
-    ms, t_lo, t_hi = time_region(step, args.steps, world)
-    tokens = Bsz * L * world
-    res = {"value": tokens * args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
-           "gpu_launches": 2 * args.steps}
-
-    # per-kernel device time, raw launches on the same inputs (live, same process)
-    A32, D32, b32 = w["A"], w["D"], w["delta_bias"]
-    keep = {}
-
-    def fwd():
-        keep["out"] = sscan_fwd_raw(w["x"], w["delta_raw"], A32, w["B"], w["C"], D32, w["z"], b32, want_carries=True)
-
-    fwd()
-    carries = keep["out"][2]
-
-    def bwd():
-        keep["g"] = sscan_bwd_raw(w["x"], w["delta_raw"], A32, w["B"], w["C"], D32, w["z"], b32, w["dy"], carries)
-
-    for f in (fwd, bwd, fwd, bwd, fwd, bwd):
-        f()
-    fwd_ms, fwd_min = time_kernel(fwd, 20)
-    bwd_ms, bwd_min = time_kernel(bwd, 20)
-    s = 2                                              # bytes per bf16 element
-    fwd_bytes = (4 * ED + 2 * N) * s * Bsz * L
-    bwd_bytes = (7 * ED + 4 * N) * s * Bsz * L
-    res["kernels"] = {
-        "sscan_fwd_kernel": {"ms": fwd_ms, "ms_min": fwd_min, "algorithmic_bytes": fwd_bytes,
-                             "GBps": fwd_bytes / fwd_ms / 1e6},
-        "sscan_bwd_kernel": {"ms": bwd_ms, "ms_min": bwd_min, "algorithmic_bytes": bwd_bytes,
-                             "GBps": bwd_bytes / bwd_ms / 1e6},
-    }
-    res["dominant"] = ("sscan_bwd_kernel", bwd_bytes, bwd_ms)
-    # dram__bytes_read.sum + dram__bytes_write.sum of one launch of that kernel on this exact workload,
-    # from the ncu capture summarised in profiles/sscan_bwd_kernel__scan_130m.md (406.6 MB + 132.0 MB;
-    # 354.4 MB algorithmic plus 201 MB of saved scan states read back)
-    res["traffic"] = 538.6e6
-    # why the HBM fraction is small: what the same capture shows to be busy instead (static figures of
-    # that capture, not re-measured here)
-    res["roofline_note"] = ("the fused backward is not HBM-bound: ncu shows DRAM at 9 % of peak while the "
-                            "shared-memory pipe is at 72 %, instruction issue at 60 %, FMA 41 %, MUFU 33 % "
-                            "(profiles/sscan_bwd_kernel__scan_130m.md)")
-
-    if args.skip_e2e:
-        sampler.stop()
-        res["clocks"] = sampler.summary(t_lo, t_hi)
-        return res
-    # end to end through the public API with host buffers: every step copies its own inputs from pinned
-    # host memory and its own results back; copies run on their own streams with two device slots, so the
-    # copies of one step overlap the compute of its neighbours (nothing is skipped or reused).
-    host_in = {k: w[k].detach().cpu().pin_memory() for k in ("x", "delta_raw", "z", "B", "C", "dy")}
-    cur = torch.cuda.current_stream()
-    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
-    slots = [{"dev": {k: torch.empty_like(w[k]) for k in host_in}, "ev_in": torch.cuda.Event(),
-              "ev_done": torch.cuda.Event(), "ev_out": torch.cuda.Event(), "outs": None, "host": None}
-             for _ in range(2)]
-    state = {"i": 0}
-    pA, pD, pb = leaves["A"].detach(), leaves["D"].detach(), leaves["delta_bias"].detach()
-
-    def e2e_step():
-        sl = slots[state["i"] % 2]
-        state["i"] += 1
-        with torch.cuda.stream(s_in):
-            s_in.wait_event(sl["ev_done"])                     # the slot's previous step has read its inputs
-            for k in host_in:
-                sl["dev"][k].copy_(host_in[k], non_blocking=True)
-            sl["ev_in"].record(s_in)
-        cur.wait_event(sl["ev_in"])
-        cur.wait_event(sl["ev_out"])                          # previous results of this slot are on the host
-        lv = {k: sl["dev"][k].requires_grad_() for k in ("x", "delta_raw", "z", "B", "C")}
-        for t in lv.values():
-            t.grad = None
-        y = mamba_b200.selective_scan_fn(lv["x"], lv["delta_raw"], pA, lv["B"], lv["C"], pD, z=lv["z"], delta_bias=pb)
-        y.backward(sl["dev"]["dy"])
-        sl["outs"] = [y.detach()] + [lv[k].grad for k in ("x", "delta_raw", "z", "B", "C")]
-        for k in lv:
-            sl["dev"][k].requires_grad_(False)
-        sl["ev_done"].record(cur)
-        if sl["host"] is None:
-            sl["host"] = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in sl["outs"]]
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(sl["ev_done"])
-            for h, o in zip(sl["host"], sl["outs"]):
-                h.copy_(o, non_blocking=True)
-            sl["ev_out"].record(s_out)
-
-    def e2e_finish():
-        cur.wait_stream(s_in)
-        cur.wait_stream(s_out)
-
-    for _ in range(3):
-        e2e_step()
-    e2e_finish()
-    k_e2e = max(8, min(args.steps, 12))          # enough steps for the two-slot pipeline to reach its steady state
-    ems, _, _ = time_region(e2e_step, k_e2e, world, finish=e2e_finish)
-    sampler.stop()
-    host_out = slots[0]["host"]
-    h2d = sum(t.numel() * t.element_size() for t in host_in.values())
-    d2h = sum(t.numel() * t.element_size() for t in host_out)
-    res["e2e"] = {"value": tokens * k_e2e / (ems * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                  "d2h_bytes_per_step": d2h, "steps": k_e2e, "ms_per_step": ems / k_e2e}
-    res["clocks"] = sampler.summary(t_lo, t_hi)
-    return res
-
-
-def bench_pscan(args, rank, world, dev):
-    import mamba_b200
-    from mamba_b200 import workloads
-    from mamba_b200.pscan import pscan_fwd_raw, pscan_bwd_raw
-    Bsz, L, D, N = 16, 2048, 1536, 16
-    A, X, G = workloads.pscan_inputs(1001 + rank, dev, Bsz, L, D, N)
-    A.requires_grad_()
-    X.requires_grad_()
-
-    def step():
-        A.grad = None
-        X.grad = None
-        mamba_b200.pscan(A, X).backward(G)
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    sampler = ClockSampler(dev.index or 0)
-    sampler.start()
-    ms, t_lo, t_hi = time_region(step, args.steps, world)
-    tokens = Bsz * L * world
-    res = {"value": tokens * args.steps / (ms * 1e-3), "ms_per_step": ms / args.steps,
-           "gpu_launches": 2 * args.steps}
-    Ad, Xd = A.detach(), X.detach()
-    keep = {}
-
-    def fwd():
-        keep["H"] = pscan_fwd_raw(Ad, Xd)[0]
-
-    fwd()
-
-    def bwd():
-        keep["g"] = pscan_bwd_raw(Ad, keep["H"], G)
-
-    for f in (fwd, bwd, fwd, bwd):
-        f()
-    fwd_ms, fwd_min = time_kernel(fwd, 10)
-    bwd_ms, bwd_min = time_kernel(bwd, 10)
-    sampler.stop()
-    elems = Bsz * L * D * N
-    res["kernels"] = {
-        "pscan_fwd_kernel": {"ms": fwd_ms, "ms_min": fwd_min, "algorithmic_bytes": 3 * elems * 4,
-                             "GBps": 3 * elems * 4 / fwd_ms / 1e6},
-        "pscan_bwd_kernel": {"ms": bwd_ms, "ms_min": bwd_min, "algorithmic_bytes": 5 * elems * 4,
-                             "GBps": 5 * elems * 4 / bwd_ms / 1e6},
-    }
-    res["dominant"] = ("pscan_bwd_kernel", 5 * elems * 4, bwd_ms)
-    # end to end with host buffers would move 12.9 GB per step over PCIe; measured on one batch row
-    hA, hX, hG = (t[:1].detach().cpu().pin_memory() for t in (A, X, G))
-    dA, dX, dG = (torch.empty_like(t[:1]) for t in (A, X, G))
-    hout = [torch.empty(hA.shape).pin_memory() for _ in range(3)]
-
-    def e2e_step():
-        dA.copy_(hA, non_blocking=True); dX.copy_(hX, non_blocking=True); dG.copy_(hG, non_blocking=True)
-        a, x = dA.requires_grad_(), dX.requires_grad_()
-        a.grad = None; x.grad = None
-        H = mamba_b200.pscan(a, x)
-        H.backward(dG)
-        for h, o in zip(hout, (H.detach(), a.grad, x.grad)):
-            h.copy_(o, non_blocking=True)
-        dA.requires_grad_(False); dX.requires_grad_(False)
-
-    for _ in range(2):
-        e2e_step()
-    k_e2e = 3
-    ems, _, _ = time_region(e2e_step, k_e2e, world)
-    per = L * D * N * 4
-    res["e2e"] = {"value": L * world * k_e2e / (ems * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": 3 * per,
-                  "d2h_bytes_per_step": 3 * per, "steps": k_e2e, "ms_per_step": ems / k_e2e,
-                  "note": "one batch row per step (B=1 of 16): the full batch would move 12.9 GB over PCIe"}
-    res["clocks"] = sampler.summary(t_lo, t_hi)
-    return res
+def roofline_of(res, peaks, peak_kind):
+    name, abytes, kms = res["dominant"]
+    achieved = abytes / kms / 1e6
+    roof = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} copy bandwidth",
+            "frac_of_nominal_8TBps": achieved / 8000.0, "traffic": res.get("traffic"),
+            "algorithmic_bytes_per_launch": abytes, "kernel_ms": kms}
+    if res.get("traffic") is not None:
+        roof["traffic_source"] = res.get("traffic_source", "static")
+    for k in ("binding", "mufu", "note"):
+        if k in res.get("roofline_extra", {}):
+            roof[k] = res["roofline_extra"][k]
+    return roof
 
 
 def main():
@@ -473,14 +340,20 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--regions", type=int, default=5, help="how many times the timed region of --steps steps is repeated")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="scan_130m", choices=["scan_130m", "pscan", "decode", "lshard", "layer"])
+    ap.add_argument("--workload", default="all", choices=["all", "scan_130m", "pscan", "decode", "lshard", "layer"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
+    ap.add_argument("--decode-layers", type=int, default=64, help="layers of the decode workload")
+    ap.add_argument("--lshard-len", type=int, default=131072, help="sequence length of the lshard workload")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    extras = args.workload == "all"
+    if extras:
+        args.workload = "scan_130m"
 
     if args.impl == "reference":
         run_reference(args, rank)
@@ -491,51 +364,57 @@ def main():
                          "(use --impl reference for the host-CPU arm)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
     if world > 1:
-        import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
+    import bench_legs as legs
+    from mamba_b200 import _lib
     wl = args.workload
-    if wl == "scan_130m":
-        res = bench_scan_130m(args, rank, world, dev)
-    elif wl == "pscan":
-        res = bench_pscan(args, rank, world, dev)
-    elif wl == "decode":
-        from mamba_b200.benchmarks import bench_decode
-        res = bench_decode(args, rank, world, dev, ClockSampler, time_region, time_kernel)
-    elif wl == "layer":
-        from mamba_b200.benchmarks import bench_layer
-        res = bench_layer(args, rank, world, dev, ClockSampler, time_region, time_kernel)
-    else:
-        from mamba_b200.benchmarks import bench_lshard
-        res = bench_lshard(args, rank, world, dev, ClockSampler, time_region, time_kernel)
-
+    res = getattr(legs, "bench_" + wl)(args, rank, world, dev, Timing)
     peaks, peak_kind = measured_peaks()
-    name, abytes, kms = res["dominant"]
-    achieved = abytes / kms / 1e6
-    roof = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-            "frac": achieved / peaks["hbm_gbs"], "peak_source": f"{peak_kind} copy bandwidth",
-            "frac_of_nominal_8TBps": achieved / 8000.0, "traffic": res.get("traffic"),
-            **({"note": res["roofline_note"]} if "roofline_note" in res else {}),
-            "algorithmic_bytes_per_launch": abytes, "kernel_ms": kms}
     line = {
         "metric": METRIC[wl], "value": res["value"], "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": res["ms_per_step"], "higher_is_better": True,
-        "scaling": SCALING[wl], "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": SCALING[wl], "vs_baseline": None, "dtype": DTYPE[wl], "reference_dtype": "f32", "data": "synthetic",
         "config": dict(workload_config(wl, world), **({"seq_len": res["seq_len"]} if "seq_len" in res else {}),
                        **({"subshards_per_gpu": res["subshards"]} if "subshards" in res else {})),
-        "roofline": roof, "kernels": res.get("kernels"),
+        "regions": res.get("regions"),
+        "roofline": roofline_of(res, peaks, peak_kind), "kernels": res.get("kernels"),
         "e2e": res.get("e2e"), "gpu_launches": res["gpu_launches"], "clocks": res.get("clocks"),
     }
+    if extras:
+        # the sequence-sharded scan at every N (its parity self-check first), then the single-GPU summaries
+        line["lshard_parity"] = legs.lshard_parity(rank, world, dev)
+        ls = legs.bench_lshard(args, rank, world, dev, Timing, summary=True)
+        line["lshard"] = {k: ls[k] for k in ("value", "ms_per_step", "regions", "passes_ms", "collective_ms",
+                                             "subshards", "seq_len", "kernels") if k in ls}
+        line["lshard"].update(unit="tokens/s", scaling="strong",
+                              roofline_frac=roofline_of(ls, peaks, peak_kind)["frac"])
+        if world == 1:
+            for name in ("pscan", "decode"):
+                r = getattr(legs, "bench_" + name)(args, rank, world, dev, Timing, summary=True)
+                roof = roofline_of(r, peaks, peak_kind)
+                line[name] = {"value": r["value"], "unit": "tokens/s", "ms_per_step": r["ms_per_step"],
+                              "dtype": DTYPE[name], "kernels": r.get("kernels"),
+                              "roofline": {k: roof[k] for k in ("kernel", "achieved", "peak", "frac")}}
+            line["b1_long"] = legs.bench_b1_long(args, dev, Timing)
+            line["reference_on_gpu"] = legs.reference_on_gpu(dev, reference_scan_fwd_bwd, Timing)
+    # a bounded wait that gave up inside a kernel leaves wrong outputs behind without any host-side error:
+    # the status word is read here, after the last synchronisation, and a non-zero word fails the run
+    status = _lib.device_status(dev)
+    line["device_status"] = status
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline and wl in CPU_SAMPLES:
             line["cpu_baseline"] = cpu_baseline(wl)
         print(json.dumps(line))
-    import torch.distributed as dist
     if dist.is_available() and dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
+    bad = status != 0 or (extras and line["lshard_parity"].get("status") != "ok")
+    if bad:
+        raise SystemExit(f"bench.py: device status {status}, lshard parity {line.get('lshard_parity')}")
 
 
 if __name__ == "__main__":

@@ -63,6 +63,12 @@ int mb200_version(void);
  * tests and diagnostics, not for the hot path.  Returns -1 if the word cannot be read. */
 int mb200_device_status(void);
 
+/* Self-test of that mechanism (no counterpart in the reference): launches one warp that waits, with
+ * the kernels' own poll-and-sleep loop but only `polls` (1 .. 2^20) polls, on a barrier nothing
+ * arrives at; it then records the give-up in the status word and returns normally.  After a
+ * synchronisation mb200_device_status() reports 1.  Nothing faults, traps or spins unbounded. */
+int mb200_selftest_wait_timeout(int polls, void* stream);
+
 /* Number of timesteps between two saved scan states ("chunk carries").  The carries
  * tensor of the fused scan has shape (B, ceil(L / chunk), ED, N), float32. */
 int mb200_sscan_chunk(void);

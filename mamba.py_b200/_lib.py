@@ -22,6 +22,7 @@ _SIGNATURES = {
     "mb200_strerror": (C.c_char_p, [_int]),
     "mb200_version": (_int, []),
     "mb200_device_status": (_int, []),
+    "mb200_selftest_wait_timeout": (_int, [_int, _ptr]),
     "mb200_sscan_chunk": (_int, []),
     "mb200_pscan_segments": (_int, [_i64] * 3),
     "mb200_pscan_fwd": (_int, [_ptr] * 3 + [_i64] * 9 + [_ptr] * 3 + [_int, _int, _ptr]),
@@ -69,6 +70,31 @@ def check(code: int, what: str) -> None:
     if code != 0:
         msg = load().mb200_strerror(code).decode()
         raise RuntimeError(f"{what} failed: {msg} (code {code})")
+
+
+def device_status(device=None) -> int:
+    """Read and clear the kernels' device-side status word on `device` (SYNCHRONISES it).
+
+    0 = every bounded wait inside the kernels launched so far completed; 1 = one gave up, and the
+    outputs of that launch are invalid.  The launches themselves never wait for this word: callers
+    poll it at their own synchronisation points (or set MB200_CHECK_STATUS=1, see check_status)."""
+    import torch
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        return load().mb200_device_status()
+
+
+CHECK_STATUS = os.environ.get("MB200_CHECK_STATUS", "0") not in ("", "0")
+
+
+def check_status(device, what: str) -> None:
+    """With MB200_CHECK_STATUS=1 in the environment every fused-scan launch is followed by a device
+    synchronisation and a read of the status word, and a give-up raises.  Off by default (it
+    serialises host and device); meant for debugging a suspected hang."""
+    if CHECK_STATUS:
+        st = device_status(device)
+        if st != 0:
+            raise RuntimeError(f"{what}: a bounded wait inside the kernel gave up (device status {st}); "
+                               "its outputs are invalid")
 
 
 def dtype_code(dtype) -> int:

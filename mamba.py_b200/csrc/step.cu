@@ -320,7 +320,43 @@ extern "C" const char* mb200_strerror(int code) {
 
 extern "C" int mb200_version(void) { return 100; }
 
+// ---- self-test of the bounded-wait mechanism -------------------------------------------------
+// One warp waits on a CTA-local mbarrier that nothing ever arrives at, with the same poll-and-sleep
+// loop the fused kernels use but a caller-chosen limit; when the polls run out it records
+// MB200_DEV_WAIT_TIMEOUT in a status word and returns.  Nothing faults and nothing spins without a
+// limit: this is how a test can see the give-up path without a broken kernel.
+namespace mb200 {
+namespace {
+__device__ int g_selftest_status = MB200_DEV_OK;
+
+__global__ void wait_timeout_selftest_kernel(int polls) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  const uint32_t addr = smem_u32(&bar);
+  bool done = mbar_poll(addr, 0);
+  for (int i = 0; i < polls && !done; ++i) {
+    __nanosleep(100);
+    done = mbar_poll(addr, 0);
+  }
+  if (!done && threadIdx.x == 0) atomicExch(&g_selftest_status, MB200_DEV_WAIT_TIMEOUT);
+}
+}  // namespace
+}  // namespace mb200
+
+extern "C" int mb200_selftest_wait_timeout(int polls, void* stream) {
+  if (polls < 1 || polls > (1 << 20)) return MB200_EINVAL;       // at most ~0.1 s of polling
+  wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(polls);
+  return check_launch();
+}
+
 extern "C" int mb200_device_status(void) {
   const int f = mb200_fwd_device_status(), b = mb200_bwd_device_status();
-  return (f < 0 || b < 0) ? -1 : (f | b);
+  int s = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&s, g_selftest_status, sizeof(int)) != cudaSuccess) return -1;
+  if (s) cudaMemcpyToSymbol(g_selftest_status, &zero, sizeof(int));
+  return (f < 0 || b < 0) ? -1 : (f | b | s);
 }

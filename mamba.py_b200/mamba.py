@@ -50,6 +50,12 @@ def _act_dtype(x: torch.Tensor, *others):
     return torch.bfloat16 if dts == {torch.bfloat16} else torch.float32
 
 
+def _tensor_map_ok(t: torch.Tensor) -> bool:
+    """16-byte aligned base and byte strides: what a tiled tensor map of a (B, L, C) tensor needs."""
+    es = t.element_size()
+    return t.data_ptr() % 16 == 0 and (t.stride(0) * es) % 16 == 0 and (t.stride(1) * es) % 16 == 0
+
+
 def _f32(t):
     return None if t is None else t.detach().float().contiguous()
 
@@ -84,6 +90,7 @@ def sscan_fwd_raw(x, delta, A, Bm, Cm, D, z=None, delta_bias=None, h0=None,
     if reverse and rc == _lib.EUNSUPPORTED:
         return None
     _lib.check(rc, "mb200_sscan_fwd")
+    _lib.check_status(dev, "mb200_sscan_fwd")
     return y, hT, carries
 
 
@@ -122,6 +129,7 @@ def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None,
             dx.stride(0), dx.stride(1), dd.stride(0), dd.stride(1), dzs[0], dzs[1],
             _lib.dtype_code(x.dtype), flags, _lib.current_stream(dev))
     _lib.check(rc, "mb200_sscan_bwd")
+    _lib.check_status(dev, "mb200_sscan_bwd")
     return dx, dd, dz, dB, dC, dA, dD, dbias, g_out
 
 
@@ -166,6 +174,10 @@ class SelectiveScanFn(torch.autograd.Function):
     def backward(ctx, dy, *unused):
         xs, ds, A32, Bs, Cs, D32, zs, b32, carries = ctx.saved_tensors
         dy = _rows(dy.flip(1) if ctx.flipped else dy, xs.dtype)
+        if ctx.reverse and not _tensor_map_ok(dy):
+            # the in-kernel reverse backward exists on the tensor-map path only; an upstream gradient
+            # that is an offset or narrow view of something wider is copied to a dense tensor first
+            dy = dy.contiguous()
         dx, dd, dz, dB, dC, dA, dD, dbias, g_out = sscan_bwd_raw(
             xs, ds, A32, Bs, Cs, D32, zs, b32, dy, carries, want_g_out=ctx.has_h0, reverse=ctx.reverse)
         if ctx.flipped:
@@ -372,7 +384,7 @@ def rms_norm(x, weight=None, eps=1e-5):
 
 def rmsnorm_forward(self, x):
     """Drop-in for RMSNorm.forward (mambapy/mamba.py:427-433)."""
-    return rms_norm(x, None if self.use_mup else self.weight, self.eps)
+    return rms_norm(x, None if getattr(self, "use_mup", False) else self.weight, self.eps)
 
 
 def _project(self, x):

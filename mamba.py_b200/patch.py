@@ -12,6 +12,7 @@ import importlib
 import sys
 
 from . import mamba as _m
+from . import vim as _v
 from .pscan import PScan as _PScan, pscan as _pscan
 
 _saved: list[tuple[object, str, object]] = []
@@ -35,7 +36,9 @@ def install(fuse_block: bool = False) -> None:
     fuse_block=False keeps MambaBlock.forward/ssm as they are and swaps only the methods whose
     signatures the reference defines (selective_scan, selective_scan_seq, ssm_step, step) plus
     pscan/PScan.  fuse_block=True also swaps MambaBlock.ssm and MambaBlock.forward for the
-    variants that run softplus, scan and gate in one kernel, and RMSNorm.forward for the one-pass kernel.
+    variants that run softplus, scan and gate in one kernel, RMSNorm.forward for the one-pass kernel,
+    and (when mambapy.vim has been imported) the bidirectional block's forward (mambapy/vim.py:205-261)
+    for one that scans the second direction in place instead of flipping the sequence.
     """
     if _saved:
         return
@@ -61,9 +64,14 @@ def install(fuse_block: bool = False) -> None:
     if fuse_block:
         _swap(blocks[0], "ssm", _m.ssm)
         _swap(blocks[0], "forward", _m.forward)
-        norm = getattr(sys.modules["mambapy.mamba"], "RMSNorm", None)
-        if norm is not None:
-            _swap(norm, "forward", _m.rmsnorm_forward)
+        for modname in ("mambapy.mamba", "mambapy.vim"):
+            norm = getattr(sys.modules.get(modname), "RMSNorm", None)
+            if norm is not None:
+                _swap(norm, "forward", _m.rmsnorm_forward)
+        vim = sys.modules.get("mambapy.vim")
+        if vim is not None and hasattr(vim, "MambaBlock"):
+            # the bidirectional block: second direction scanned right-to-left inside the kernels
+            _swap(vim.MambaBlock, "forward", _v.forward)
 
 
 def uninstall() -> None:

@@ -78,3 +78,17 @@ def assert_close(got, want, rtol, atol, msg=""):
     got = got.detach().float().cpu().numpy() if torch.is_tensor(got) else got
     want = want.detach().float().cpu().numpy() if torch.is_tensor(want) else want
     np.testing.assert_allclose(got, want, rtol=rtol, atol=atol, err_msg=msg)
+
+
+def oracle_f64_blocked(inp, gated=True, bias=None, block=512):
+    """Float64 oracle (outputs and every gradient) for WIDE problems: the closed-form forward/backward
+    of the oracle, run `block` channels at a time (oracle.selective_scan_fwd_bwd_f64).
+
+    inp: dict of float tensors x, delta, z, gy (B, L, ED), B, C (B, L, N), A (ED, N), D (ED);
+    bias (ED) optional: delta is then raw and softplus(delta + bias) is applied by the oracle.
+    Returns (y, grads) with grads keyed x, delta, B, C, A, D (and z, bias)."""
+    from oracle import scan_oracle as O
+    y, _, grads = O.selective_scan_fwd_bwd_f64(inp["x"], inp["delta"], inp["A"], inp["B"], inp["C"], inp["D"],
+                                               inp["gy"], z=inp["z"] if gated else None, delta_bias=bias,
+                                               block=block)
+    return y, grads

@@ -70,6 +70,11 @@ def test_noalloc_matches_plain_entry_point_twice():
         H1, h1 = torch.empty_like(X), torch.empty_like(hT_ref)
         assert _call_plain(lib, A, X, H1, h1, 1) == 0
         assert torch.allclose(H, H1, rtol=1e-4, atol=1e-5)
+        # and against the CPU oracle's sequential loop, so this file stands on its own
+        from oracle import scan_oracle as O
+        Hs = O.scan_sequential(A.cpu().double(), X.cpu().double())
+        assert torch.allclose(H.cpu().double(), Hs, rtol=1e-4, atol=1e-5)
+        assert torch.allclose(hT.cpu().double(), Hs[:, -1].reshape(shape[0], -1), rtol=1e-4, atol=1e-5)
 
 
 def test_noalloc_library_choice_and_limit():
@@ -81,9 +86,13 @@ def test_noalloc_library_choice_and_limit():
     assert _call_plain(lib, A, X, H1, h1, 1) == 0
     torch.cuda.synchronize()
     assert torch.allclose(H, H1, rtol=1e-4, atol=1e-5)
-    # a request whose aggregates cannot fit the fixed array is refused, nothing is launched
-    big = (4, 4096, 1024, 16)                                 # 2*4*64*16384 floats = 8.4 M > 2 M
-    fake = torch.empty(1, device=DEV)                          # never dereferenced: refused first
-    rc = lib.mb200_pscan_fwd_noalloc(fake.data_ptr(), fake.data_ptr(), fake.data_ptr(), big[0], big[1],
-                                     big[2] * big[3], 1, 1, 1, 1, 1, 1, None, None, 64, _lib.F32, None)
+    # a request whose aggregates cannot fit the fixed array is refused and nothing is launched.  The
+    # buffers are real and large enough for the call, so that a regression of the limit check would
+    # show up as a wrong return code, not as an out-of-bounds access.
+    big = (1, 64, 1024, 16)                                   # nseg 65: 2*1*65*16384 floats > 2^21
+    Ab, Xb = _inputs(4, big)
+    Hb, hb = torch.empty_like(Xb), torch.empty(1, big[2] * big[3], device=DEV)
+    assert 2 * big[0] * 65 * big[2] * big[3] > lib.mb200_pscan_noalloc_max_ws_floats()
+    rc = _call_noalloc(lib, Ab, Xb, Hb, hb, 65)
+    torch.cuda.synchronize()
     assert rc == -6 and b"limit" in lib.mb200_strerror(rc)
