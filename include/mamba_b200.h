@@ -44,6 +44,12 @@ enum {
 enum {
   MB200_DELTA_SOFTPLUS = 1, /* delta = softplus(delta_raw + delta_bias[e]) is applied inside;
                                without it `delta` is taken as already discretised           */
+  MB200_GENERAL_DECAY = 4,  /* evaluate every decay exp(delta*A[e,n]) with its own ex2.  Without this
+                               flag the kernels notice (per warp, on the device) when the rows of A they
+                               own follow the S4D-real structure A[e,n] = (n+1)*A[e,0] to within 2^-20
+                               relative (the reference's initialisation, mambapy/mamba.py:168-169) and
+                               then form the four decays of a state quad from two ex2 and three
+                               multiplies; any other A takes the general path on its own.            */
   MB200_REVERSE = 2         /* scan from t = L-1 down to 0 (h[t] = a[t] h[t+1] + ...): what the
                                reference's bidirectional model gets by flipping the sequence,
                                scanning and flipping back (mambapy/vim.py:228-261).  h0 is then the

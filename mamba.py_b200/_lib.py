@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(HERE, "libmamba_b200.so")
 F32, BF16 = 0, 1
 DELTA_SOFTPLUS = 1
 REVERSE = 2
+GENERAL_DECAY = 4
 EUNSUPPORTED = -8
 
 _i64, _int, _ptr = C.c_int64, C.c_int, C.c_void_p

@@ -24,6 +24,7 @@
 //     store of its partial C-contraction.
 //   - Hand-off through CTA-local mbarriers.  Every wait is bounded: a wait that gives up records
 //     MB200_DEV_WAIT_TIMEOUT and the thread leaves the kernel, so nothing can spin forever.
+#include <type_traits>
 #include "sscan_fwd_generic.cuh"
 #include "tma.cuh"
 
@@ -33,18 +34,47 @@ namespace {
 // Raw-tile ring depth.  Copies are issued kStages - 2 tiles ahead: a box takes a few microseconds
 // to land, several times the ~1 us a tile is worked on, so the ring must hold that many in flight.
 template <typename T> struct Ring { static constexpr int kStages = sizeof(T) == 2 ? 8 : 5; };
-constexpr int kTmaProducers = 128;
-constexpr int kTmaThreads = kConsumers + kTmaProducers;
 constexpr int kTile = 2 * kChunk;          // timesteps per tile (two saved states per tile)
+
+// Geometry of one CTA: kCW consumer warps whose threads each own 4 consecutive states of kCPT
+// neighbouring channels, and kPW producer warps.  What a consumer thread pulls out of shared memory per
+// element is 8/kCPT bytes of B and C plus 2 bytes of {delta, delta*x}: two channels per thread (d_state
+// 16) cut the recurrence's shared-memory traffic from 11 to 7 bytes per element, which is what bounds it.
+#ifndef MB200_FWD_CW
+#define MB200_FWD_CW 3
+#endif
+#ifndef MB200_FWD_CPT
+#define MB200_FWD_CPT 2
+#endif
+#ifndef MB200_FWD_PW
+#define MB200_FWD_PW 4
+#endif
+#ifndef MB200_FWD_OCC
+#define MB200_FWD_OCC 2
+#endif
+template <int N> struct FwdGeom {
+  static constexpr int kCPT = (N == 16) ? MB200_FWD_CPT : 1;
+  static constexpr int kCW = (N == 16) ? MB200_FWD_CW : 4;
+  static constexpr int kPW = (N == 16) ? MB200_FWD_PW : 4;
+  static constexpr int kOcc = (N == 16) ? MB200_FWD_OCC : 3;          // CTAs per SM the kernel is compiled for
+  static constexpr int kLPE = N / 4;                                   // lanes per channel group
+  static constexpr int kConsumers = 32 * kCW;
+  static constexpr int kProducers = 32 * kPW;
+  static constexpr int kThreads = kConsumers + kProducers;
+  static constexpr int kTE = kConsumers / kLPE * kCPT;                 // channels per CTA
+  static_assert(kCPT == 1 || (kCPT == 2 && N == 16), "two channels per thread are laid out for d_state 16");
+  static_assert(kTE % 8 == 0, "a tile row is a whole number of 16-byte vectors in bf16");
+};
 
 struct FwdMaps {
   CUtensorMap x, d, z, B, C;
 };
 
 template <typename T, int N> struct TmaFwdSmem {
-  using G = SscanGeom<N>;
+  using G = FwdGeom<N>;
   static constexpr int kStages = Ring<T>::kStages;
   static constexpr int kTE = G::kTE;
+  static constexpr int kYpRow = kTE * G::kLPE;                          // partial sums per timestep
   static constexpr int kActBytes = kTile * kTE * int(sizeof(T));       // one raw x / delta / z box
   static constexpr int kBcBytes = kTile * N * int(sizeof(T));          // one raw B / C box
   static constexpr int kStageBytes = 3 * kActBytes + 2 * kBcBytes;
@@ -54,12 +84,46 @@ template <typename T, int N> struct TmaFwdSmem {
   static constexpr int kOp = kRaw + kStages * kStageBytes;              // float2 [2][kTile][kTE]
   static constexpr int kB = kOp + 2 * kTile * kTE * 8;                  // float  [2][kTile][N]
   static constexpr int kC = kB + 2 * kTile * N * 4;
-  static constexpr int kYp = kC + 2 * kTile * N * 4;                    // float  [2][kTile][128]
-  static constexpr int kD = kYp + 2 * kTile * kConsumers * 4;           // float  [kTE]
+  static constexpr int kYp = kC + 2 * kTile * N * 4;                    // float  [2][kTile][kYpRow]
+  static constexpr int kD = kYp + 2 * kTile * kYpRow * 4;               // float  [kTE]
   static constexpr int kBias = kD + kTE * 4;
   static constexpr int kBars = kBias + kTE * 4;                         // (2*kStages + 4) x uint64
   static constexpr int kBytes = kBars + (2 * kStages + 4) * 8;
 };
+
+// The decays a[j] = exp(delta * A[4q + j]), j = 0..3, of one channel.  General form: four ex2.
+// With the S4D-real structure A[e, n] = (n + 1) A[e, 0] (the reference's initialisation,
+// mambapy/mamba.py:168-169) they are p, p r, p r^2, p r^3 with r = exp(delta A[e, 0]) and
+// p = exp(delta A[e, 4q]): two ex2 and three multiplies, which halves the load on the MUFU pipe.
+template <bool kStruct>
+__device__ __forceinline__ void decay4(float dl, const float2& A2lo, const float2& A2hi, float A0, float2& a_lo,
+                                       float2& a_hi) {
+  const float2 dd = make_float2(dl, dl);
+  if constexpr (!kStruct) {
+    const float2 e_lo = __fmul2_rn(dd, A2lo), e_hi = __fmul2_rn(dd, A2hi);
+    a_lo = make_float2(ex2f(e_lo.x), ex2f(e_lo.y));
+    a_hi = make_float2(ex2f(e_hi.x), ex2f(e_hi.y));
+  } else {
+    const float2 e = __fmul2_rn(dd, make_float2(A0, A2lo.x));
+    const float r = ex2f(e.x), p1 = ex2f(e.y);
+    const float r2 = r * r;
+    a_lo = make_float2(p1, p1 * r);
+    a_hi = __fmul2_rn(a_lo, make_float2(r2, r2));
+  }
+}
+
+// True when the 4 states 4q .. 4q+3 of a row of A (scaled by log2 e or not) follow A[n] = (n + 1) A[0]
+// to within 2^-20 relative: a perturbation of the decay RATE of at most 1e-6, below the error of
+// ex2.approx on the general path (libm's exp(log(n)) is not exactly n, so exact equality never holds).
+__device__ __forceinline__ bool s4d_structured(const float* a4, float a0, int q) {
+  bool ok = true;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float want = float(4 * q + j + 1) * a0;
+    ok = ok && fabsf(a4[j] - want) <= 9.5367431640625e-7f * fabsf(want);
+  }
+  return ok;
+}
 
 // kCarry turns the kernel into the reverse carry pass of the sequence-sharded backward
 // (gc <- a[t] * (dy'[t] * C[t] + gc), t = L-1 ... 0): the caller passes dy as `x` and C as `Bm`, the
@@ -67,11 +131,12 @@ template <typename T, int N> struct TmaFwdSmem {
 // after adding the input.  It has no y and saves no states; the result leaves through hT.
 // kHasY = false is the pass that only wants states (no C-contraction, no epilogue).
 template <typename T, int N, bool kRev, bool kCarry, bool kHasY>
-__global__ void __launch_bounds__(kTmaThreads, 3)
+__global__ void __launch_bounds__(FwdGeom<N>::kThreads, FwdGeom<N>::kOcc)
 sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams p) {
-  using G = SscanGeom<N>;
+  using G = FwdGeom<N>;
   using S = TmaFwdSmem<T, N>;
   constexpr int kLPE = G::kLPE, kTE = G::kTE, kStages = S::kStages, kAhead = S::kStages - 2;
+  constexpr int kCPT = G::kCPT, kNC = G::kConsumers, kNP = G::kProducers, kYpRow = S::kYpRow;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
   float2* s_op = reinterpret_cast<float2*>(smem_raw + S::kOp);
@@ -103,92 +168,136 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
 
   if (tid == 0) {
 #pragma unroll
-    for (int i = 0; i < kStages; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_free[i], kTmaProducers); }
-    mbar_init(&op_full[0], kTmaProducers); mbar_init(&op_full[1], kTmaProducers);
-    mbar_init(&op_empty[0], kConsumers); mbar_init(&op_empty[1], kConsumers);
+    for (int i = 0; i < kStages; ++i) { mbar_init(&raw_full[i], 1); mbar_init(&raw_free[i], kNP); }
+    mbar_init(&op_full[0], kNP); mbar_init(&op_full[1], kNP);
+    mbar_init(&op_empty[0], kNC); mbar_init(&op_empty[1], kNC);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int i = tid; i < kTE; i += kTmaThreads) {
+  for (int i = tid; i < kTE; i += G::kThreads) {
     const bool ok = i < cols_ok;
     s_D[i] = (ok && p.D) ? p.D[e0 + i] : 0.f;
     s_bias[i] = (ok && softplus) ? p.delta_bias[e0 + i] : 0.f;
   }
   __syncthreads();
 
-  if (tid < kConsumers) {
+  if (tid < kNC) {
     // ------------------------------------------------------------------ consumers
-    const int e_l = tid / kLPE, q = tid % kLPE;
-    const int64_t e = e0 + e_l;
-    const bool e_ok = e < p.ED;
-    float2 A2lo, A2hi, hlo, hhi;
-    {
+    const int grp = tid / kLPE, q = tid % kLPE;        // channel group (kCPT channels) and state quad
+    const int e_l = grp * kCPT;                        // first channel of this thread inside the tile
+    float2 A2lo[kCPT], A2hi[kCPT], hlo[kCPT], hhi[kCPT];
+    float A0[kCPT];
+    bool e_ok[kCPT];
+    bool structured = (p.flags & MB200_GENERAL_DECAY) == 0;
+#pragma unroll
+    for (int i = 0; i < kCPT; ++i) {
+      const int64_t e = e0 + e_l + i;
+      e_ok[i] = e < p.ED;
       float a4[4], h4[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        a4[j] = e_ok ? p.A[e * N + 4 * q + j] * kLog2e : 0.f;
-        h4[j] = (e_ok && p.h0) ? p.h0[(b * p.ED + e) * N + 4 * q + j] : 0.f;
+        a4[j] = e_ok[i] ? p.A[e * N + 4 * q + j] * kLog2e : 0.f;
+        h4[j] = (e_ok[i] && p.h0) ? p.h0[(b * p.ED + e) * N + 4 * q + j] : 0.f;
       }
-      A2lo = make_float2(a4[0], a4[1]); A2hi = make_float2(a4[2], a4[3]);
-      hlo = make_float2(h4[0], h4[1]); hhi = make_float2(h4[2], h4[3]);
+      A0[i] = e_ok[i] ? p.A[e * N] * kLog2e : 0.f;
+      structured = structured && s4d_structured(a4, A0[i], q);
+      A2lo[i] = make_float2(a4[0], a4[1]); A2hi[i] = make_float2(a4[2], a4[3]);
+      hlo[i] = make_float2(h4[0], h4[1]); hhi[i] = make_float2(h4[2], h4[3]);
     }
+    structured = __all_sync(0xffffffffu, structured);          // one code path per warp
     const int op_off0 = op_index(0, e_l, kTE), op_off1 = op_index(1, e_l, kTE) - kTE;
-    const int yp_off0 = yp_slot<kLPE, kTE>(0, e_l) * kLPE + q;
-    const int yp_off1 = yp_slot<kLPE, kTE>(1, e_l) * kLPE + q;
+    // where this thread leaves its partial C-contractions inside a timestep's row of partial sums
+    int yp_off0, yp_off1;
+    if constexpr (kCPT == 1) {
+      yp_off0 = yp_slot<kLPE, kTE>(0, e_l) * kLPE + q;
+      yp_off1 = yp_slot<kLPE, kTE>(1, e_l) * kLPE + q;
+    } else {
+      yp_off0 = yp_off1 = ((e_l >> 2) * 4 + q) * 4 + (e_l & 3);   // [channel quad][q][channel in quad]
+    }
     const int64_t nchunks = (p.L + kChunk - 1) / kChunk;
-    float* carry_base = (p.carries && e_ok) ? p.carries + (b * nchunks * p.ED + e) * N + 4 * q : nullptr;
+    float* carry_base = p.carries ? p.carries + (b * nchunks * p.ED + e0 + e_l) * N + 4 * q : nullptr;
     // row of processing step t is rb0 + t * rstep (in operand-tile rows); odd rows use the other swizzle offset
     constexpr int rb0 = rev ? kTile - 1 : 0, rstep = rev ? -1 : 1;
     const int off_even = rev ? op_off1 : op_off0, off_odd = rev ? op_off0 : op_off1;
 
-    for (int64_t kt = 0; kt < ntiles; ++kt) {
-      const int buf = int(kt & 1);
-      if (!mbar_wait(&op_full[buf], int((kt >> 1) & 1))) {
-        atomicExch(&g_fwd_status, MB200_DEV_WAIT_TIMEOUT);
-        return;
-      }
-      const int64_t t0a = tile_t0(kt);
-      const float2* op = s_op + buf * kTile * kTE;
-      const float* sB = s_B + buf * kTile * N + 4 * q;
-      const float* sC = s_C + buf * kTile * N + 4 * q;
-      float* yp = s_yp + buf * kTile * kConsumers;
-#pragma unroll
-      for (int t = 0; t < kTile; ++t) {
-        if (t % kChunk == 0 && carry_base) {                              // state entering this chunk
-          const int64_t c = t0a / kChunk + (rev ? 1 - t / kChunk : t / kChunk);
-          if (c < nchunks)
-            *reinterpret_cast<float4*>(carry_base + c * p.ED * N) = make_float4(hlo.x, hlo.y, hhi.x, hhi.y);
+    auto run_tiles = [&](auto struct_tag) {
+      constexpr bool kStruct = decltype(struct_tag)::value;
+      for (int64_t kt = 0; kt < ntiles; ++kt) {
+        const int buf = int(kt & 1);
+        if (!mbar_wait(&op_full[buf], int((kt >> 1) & 1))) {
+          atomicExch(&g_fwd_status, MB200_DEV_WAIT_TIMEOUT);
+          return false;
         }
-        const int r = rb0 + t * rstep;
-        const float2 o = op[r * kTE + ((t & 1) ? off_odd : off_even)];   // {delta, delta*x}
-        const float4 Bq = *reinterpret_cast<const float4*>(sB + r * N);
-        float4 Cq = Bq;
-        if constexpr (kHasY) Cq = *reinterpret_cast<const float4*>(sC + r * N);
-        const float2 dd = make_float2(o.x, o.x), dxx = make_float2(o.y, o.y);
-        const float2 e_lo = __fmul2_rn(dd, A2lo), e_hi = __fmul2_rn(dd, A2hi);
-        const float2 a_lo = make_float2(ex2f(e_lo.x), ex2f(e_lo.y));
-        const float2 a_hi = make_float2(ex2f(e_hi.x), ex2f(e_hi.y));
-        if constexpr (kCarry) {
-          hlo = __fmul2_rn(a_lo, __ffma2_rn(dxx, make_float2(Bq.x, Bq.y), hlo));
-          hhi = __fmul2_rn(a_hi, __ffma2_rn(dxx, make_float2(Bq.z, Bq.w), hhi));
-        } else {
-          const float2 u_lo = __fmul2_rn(dxx, make_float2(Bq.x, Bq.y));
-          const float2 u_hi = __fmul2_rn(dxx, make_float2(Bq.z, Bq.w));
-          hlo = __ffma2_rn(a_lo, hlo, u_lo);
-          hhi = __ffma2_rn(a_hi, hhi, u_hi);
-          if constexpr (kHasY) {
-            float2 acc = __fmul2_rn(hlo, make_float2(Cq.x, Cq.y));
-            acc = __ffma2_rn(hhi, make_float2(Cq.z, Cq.w), acc);
-            yp[t * kConsumers + ((t & 1) ? yp_off1 : yp_off0)] = acc.x + acc.y;
+        const int64_t t0a = tile_t0(kt);
+        const float2* op = s_op + buf * kTile * kTE;
+        const float* sB = s_B + buf * kTile * N + 4 * q;
+        const float* sC = s_C + buf * kTile * N + 4 * q;
+        float* yp = s_yp + buf * kTile * kYpRow;
+#pragma unroll
+        for (int t = 0; t < kTile; ++t) {
+          if (t % kChunk == 0 && carry_base) {                              // state entering this chunk
+            const int64_t c = t0a / kChunk + (rev ? 1 - t / kChunk : t / kChunk);
+            if (c < nchunks) {
+#pragma unroll
+              for (int i = 0; i < kCPT; ++i)
+                if (e_ok[i])
+                  *reinterpret_cast<float4*>(carry_base + (c * p.ED + i) * N) =
+                      make_float4(hlo[i].x, hlo[i].y, hhi[i].x, hhi[i].y);
+            }
+          }
+          const int r = rb0 + t * rstep;
+          float2 o[kCPT];                                                    // {delta, delta*x} per channel
+          if constexpr (kCPT == 1) {
+            o[0] = op[r * kTE + ((t & 1) ? off_odd : off_even)];
+          } else {
+            const float4 o4 = *reinterpret_cast<const float4*>(op + r * kTE + ((t & 1) ? off_odd : off_even));
+            o[0] = make_float2(o4.x, o4.y); o[1] = make_float2(o4.z, o4.w);
+          }
+          const float4 Bq = *reinterpret_cast<const float4*>(sB + r * N);
+          float4 Cq = Bq;
+          if constexpr (kHasY) Cq = *reinterpret_cast<const float4*>(sC + r * N);
+          float ysum[kCPT];
+#pragma unroll
+          for (int i = 0; i < kCPT; ++i) {
+            const float2 dxx = make_float2(o[i].y, o[i].y);
+            float2 a_lo, a_hi;
+            decay4<kStruct>(o[i].x, A2lo[i], A2hi[i], A0[i], a_lo, a_hi);
+            if constexpr (kCarry) {
+              hlo[i] = __fmul2_rn(a_lo, __ffma2_rn(dxx, make_float2(Bq.x, Bq.y), hlo[i]));
+              hhi[i] = __fmul2_rn(a_hi, __ffma2_rn(dxx, make_float2(Bq.z, Bq.w), hhi[i]));
+            } else {
+              const float2 u_lo = __fmul2_rn(dxx, make_float2(Bq.x, Bq.y));
+              const float2 u_hi = __fmul2_rn(dxx, make_float2(Bq.z, Bq.w));
+              hlo[i] = __ffma2_rn(a_lo, hlo[i], u_lo);
+              hhi[i] = __ffma2_rn(a_hi, hhi[i], u_hi);
+              if constexpr (kHasY) {
+                float2 acc = __fmul2_rn(hlo[i], make_float2(Cq.x, Cq.y));
+                acc = __ffma2_rn(hhi[i], make_float2(Cq.z, Cq.w), acc);
+                ysum[i] = acc.x + acc.y;
+              }
+            }
+          }
+          if constexpr (kHasY && !kCarry) {
+            float* dst = yp + t * kYpRow + ((t & 1) ? yp_off1 : yp_off0);
+            if constexpr (kCPT == 1) *dst = ysum[0];
+            else *reinterpret_cast<float2*>(dst) = make_float2(ysum[0], ysum[1]);
           }
         }
+        mbar_arrive(&op_empty[buf]);
       }
-      mbar_arrive(&op_empty[buf]);
+      return true;
+    };
+    const bool ok = structured ? run_tiles(std::true_type{}) : run_tiles(std::false_type{});
+    if (!ok) return;
+    if (p.hT) {
+#pragma unroll
+      for (int i = 0; i < kCPT; ++i)
+        if (e_ok[i])
+          *reinterpret_cast<float4*>(p.hT + (b * p.ED + e0 + e_l + i) * N + 4 * q) =
+              make_float4(hlo[i].x, hlo[i].y, hhi[i].x, hhi[i].y);
     }
-    if (p.hT && e_ok)
-      *reinterpret_cast<float4*>(p.hT + (b * p.ED + e) * N + 4 * q) = make_float4(hlo.x, hlo.y, hhi.x, hhi.y);
   } else {
     // ------------------------------------------------------------------ producers
-    const int pt = tid - kConsumers;
+    const int pt = tid - kNC;
     constexpr int kVecs = kTile * kTE / 4;                 // 4-channel vectors per activation tile
     constexpr int kVecPerRow = kTE / 4;
     T* gy = has_y ? static_cast<T*>(p.y) + b * p.y_sb + e0 : nullptr;
@@ -219,7 +328,7 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
       const T* rx = reinterpret_cast<const T*>(st);
       const T* rd = reinterpret_cast<const T*>(st + S::kActBytes);
       float2* tile = s_op + buf * kTile * kTE;
-      for (int v = pt; v < kVecs; v += kTmaProducers) {
+      for (int v = pt; v < kVecs; v += kNP) {
         const int rr = v / kVecPerRow, cc = (v % kVecPerRow) * 4;
         const Vec4<T> xv = *reinterpret_cast<const Vec4<T>*>(rx + rr * kTE + cc);
         const Vec4<T> dv4 = *reinterpret_cast<const Vec4<T>*>(rd + rr * kTE + cc);
@@ -251,7 +360,7 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
       float* dstB = s_B + buf * kTile * N;
       float* dstC = s_C + buf * kTile * N;
       constexpr int kBcVecs = kTile * N / 4;
-      for (int v = pt; v < 2 * kBcVecs; v += kTmaProducers) {
+      for (int v = pt; v < 2 * kBcVecs; v += kNP) {
         const Vec4<T> r4 = *reinterpret_cast<const Vec4<T>*>(rB + v * 4);
         float* dst = (v < kBcVecs) ? dstB + v * 4 : dstC + (v - kBcVecs) * 4;
         *reinterpret_cast<float4*>(dst) = make_float4(Elem<T>::to_f(r4.v[0]), Elem<T>::to_f(r4.v[1]),
@@ -266,19 +375,35 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
       const unsigned char* st = stage_ptr(kt);
       const T* rx = reinterpret_cast<const T*>(st);
       const T* rz = reinterpret_cast<const T*>(st + 2 * S::kActBytes);
-      const float* yp = s_yp + buf * kTile * kConsumers;
-      for (int v = pt; v < kVecs; v += kTmaProducers) {
+      const float* yp = s_yp + buf * kTile * kYpRow;
+      for (int v = pt; v < kVecs; v += kNP) {
         const int rr = v / kVecPerRow, cc = (v % kVecPerRow) * 4;
         if (rr >= rows_ok || cc >= cols_ok) continue;
         const Vec4<T> xv = *reinterpret_cast<const Vec4<T>*>(rx + rr * kTE + cc);
         Vec4<T> zv = xv;
         if (has_z) zv = *reinterpret_cast<const Vec4<T>*>(rz + rr * kTE + cc);
+        const int ps = rev ? kTile - 1 - rr : rr;            // processing step that produced row rr
+        float s4[4];
+        if constexpr (kCPT == 1) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            s4[k] = sum_lanes<kLPE>(yp + ps * kYpRow + yp_slot<kLPE, kTE>(ps, cc + k) * kLPE);
+        } else {
+          // the four state quads' partials of channels cc .. cc+3 are four 16-byte vectors; lanes start at
+          // different ones so that a quarter-warp's loads fall into different banks
+          const float4* quad = reinterpret_cast<const float4*>(yp + ps * kYpRow + cc * 4);
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 w = quad[(j + (pt >> 1)) & 3];
+            acc.x += w.x; acc.y += w.y; acc.z += w.z; acc.w += w.w;
+          }
+          s4[0] = acc.x; s4[1] = acc.y; s4[2] = acc.z; s4[3] = acc.w;
+        }
         Vec4<T> out;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const int ps = rev ? kTile - 1 - rr : rr;          // processing step that produced row rr
-          const float s = sum_lanes<kLPE>(yp + ps * kConsumers + yp_slot<kLPE, kTE>(ps, cc + k) * kLPE);
-          float yv = fmaf(s_D[cc + k], Elem<T>::to_f(xv.v[k]), s);
+          float yv = fmaf(s_D[cc + k], Elem<T>::to_f(xv.v[k]), s4[k]);
           if (has_z) {
             const float zf = Elem<T>::to_f(zv.v[k]);
             yv *= zf * sigmoid_fast(zf);
@@ -320,7 +445,7 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
 
 template <typename T, int N>
 int tma_launch_n(const SscanFwdParams& p, cudaStream_t st) {
-  using G = SscanGeom<N>;
+  using G = FwdGeom<N>;
   using S = TmaFwdSmem<T, N>;
   constexpr bool bf = sizeof(T) == 2;
   FwdMaps m;
@@ -338,7 +463,7 @@ int tma_launch_n(const SscanFwdParams& p, cudaStream_t st) {
   if (cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes) != cudaSuccess)
     return MB200_ELAUNCH;
   dim3 grid(unsigned((p.ED + G::kTE - 1) / G::kTE), unsigned(p.B));
-  k<<<grid, kTmaThreads, S::kBytes, st>>>(m, p);
+  k<<<grid, G::kThreads, S::kBytes, st>>>(m, p);
   return check_launch();
 }
 
@@ -355,7 +480,7 @@ int tma_launch_t(const SscanFwdParams& p, int N, cudaStream_t st) {
 
 // The tensor-map path needs 16-byte aligned bases and byte strides, and 8-byte aligned y rows.
 bool tma_path_ok(const SscanFwdParams& p, int N, int es) {
-  const int te = kThreadsPerCta / (N / 4);
+  const int te = N == 8 ? FwdGeom<8>::kTE : N == 16 ? FwdGeom<16>::kTE : N == 32 ? FwdGeom<32>::kTE : FwdGeom<64>::kTE;
   if (p.L >= (int64_t(1) << 31) || p.ED >= (int64_t(1) << 31)) return false;
   bool ok = tma_compatible(p.x, p.x_sb, p.x_sl, p.ED, es, te) &&
             tma_compatible(p.delta, p.d_sb, p.d_sl, p.ED, es, te) &&

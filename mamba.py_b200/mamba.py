@@ -61,12 +61,13 @@ def _f32(t):
 
 
 def sscan_fwd_raw(x, delta, A, Bm, Cm, D, z=None, delta_bias=None, h0=None,
-                  want_last=False, want_carries=False, want_y=True, reverse=False):
+                  want_last=False, want_carries=False, want_y=True, reverse=False, general_decay=False):
     """Launch the fused forward.  Tensors must already be prepared by the caller.
 
     Returns (y, hT, carries); entries not asked for are None.  With `reverse` the scan runs from the
     last timestep to the first; None is returned when the kernels cannot do that for these tensors
-    (the caller then flips them itself)."""
+    (the caller then flips them itself).  `general_decay` switches off the kernels' own shortcut for an
+    A with the S4D-real structure (every decay then gets its own exponential)."""
     lib = _lib.load()
     Bsz, L, ED = x.shape
     N = A.shape[1]
@@ -76,7 +77,8 @@ def sscan_fwd_raw(x, delta, A, Bm, Cm, D, z=None, delta_bias=None, h0=None,
     chunk = lib.mb200_sscan_chunk()
     carries = (torch.empty((Bsz, (L + chunk - 1) // chunk, ED, N), dtype=torch.float32, device=dev)
                if want_carries else None)
-    flags = (_lib.DELTA_SOFTPLUS if delta_bias is not None else 0) | (_lib.REVERSE if reverse else 0)
+    flags = ((_lib.DELTA_SOFTPLUS if delta_bias is not None else 0) | (_lib.REVERSE if reverse else 0)
+             | (_lib.GENERAL_DECAY if general_decay else 0))
     zs = (z.stride(0), z.stride(1)) if z is not None else (0, 0)
     ys = (y.stride(0), y.stride(1)) if y is not None else (0, 0)
     with torch.cuda.device(dev):
@@ -95,7 +97,7 @@ def sscan_fwd_raw(x, delta, A, Bm, Cm, D, z=None, delta_bias=None, h0=None,
 
 
 def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None, want_g_out=False,
-                  reverse=False):
+                  reverse=False, general_decay=False):
     """Launch the fused backward.  Returns (dx, ddelta, dz, dB, dC, dA, dD, dbias, g_out).
 
     `reverse` must be what the forward that produced `carries` ran with."""
@@ -115,7 +117,8 @@ def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None,
     dD = acc[2 * nBC + nA:2 * nBC + nA + ED]
     dbias = acc[2 * nBC + nA + ED:] if delta_bias is not None else None
     g_out = torch.empty((Bsz, ED, N), dtype=torch.float32, device=dev) if want_g_out else None
-    flags = (_lib.DELTA_SOFTPLUS if delta_bias is not None else 0) | (_lib.REVERSE if reverse else 0)
+    flags = ((_lib.DELTA_SOFTPLUS if delta_bias is not None else 0) | (_lib.REVERSE if reverse else 0)
+             | (_lib.GENERAL_DECAY if general_decay else 0))
     zs = (z.stride(0), z.stride(1)) if z is not None else (0, 0)
     dzs = (dz.stride(0), dz.stride(1)) if dz is not None else (0, 0)
     with torch.cuda.device(dev):
