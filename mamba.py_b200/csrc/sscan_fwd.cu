@@ -38,19 +38,24 @@ constexpr int kTile = 2 * kChunk;          // timesteps per tile (two saved stat
 
 // Geometry of one CTA: kCW consumer warps whose threads each own 4 consecutive states of kCPT
 // neighbouring channels, and kPW producer warps.  What a consumer thread pulls out of shared memory per
-// element is 8/kCPT bytes of B and C plus 2 bytes of {delta, delta*x}: two channels per thread (d_state
-// 16) cut the recurrence's shared-memory traffic from 11 to 7 bytes per element, which is what bounds it.
+// element is 8/kCPT bytes of B and C plus 2 bytes of {delta, delta*x}, so two channels per thread (d_state
+// 16) cut the recurrence's shared-memory traffic from 11 to 7 bytes per element -- and halve the number of
+// warps that run it.  Measured on the 130m layer shape (B 8, L 2048, ED 1536, bf16), forward with saved
+// states: 4 warps x 1 channel, 3 CTAs/SM 0.226 ms; 3 warps x 2 channels (48-channel CTAs, 2 per SM)
+// 0.246 ms; 4 x 2 (64-channel CTAs) 0.283 ms; 2 x 2 (32-channel CTAs, 4 per SM) 0.263 ms.  The recurrence
+// warps are in-order and wait on the loaded shared-memory pipe's round trip, so the count of resident
+// warps matters more than the bytes: one channel per thread stays the default.
 #ifndef MB200_FWD_CW
-#define MB200_FWD_CW 3
+#define MB200_FWD_CW 4
 #endif
 #ifndef MB200_FWD_CPT
-#define MB200_FWD_CPT 2
+#define MB200_FWD_CPT 1
 #endif
 #ifndef MB200_FWD_PW
 #define MB200_FWD_PW 4
 #endif
 #ifndef MB200_FWD_OCC
-#define MB200_FWD_OCC 2
+#define MB200_FWD_OCC 3
 #endif
 template <int N> struct FwdGeom {
   static constexpr int kCPT = (N == 16) ? MB200_FWD_CPT : 1;

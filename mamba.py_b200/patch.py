@@ -52,10 +52,10 @@ def install(fuse_block: bool = False) -> None:
         if mod is not None and hasattr(mod, "pscan"):
             _swap(mod, "pscan", _pscan)
     blocks = [sys.modules["mambapy.mamba"].MambaBlock]
-    for modname in ("mambapy.vim", "mambapy.onnx.mamba_onnx"):
+    for modname, cls in (("mambapy.vim", "VMambaBlock"), ("mambapy.onnx.mamba_onnx", "MambaBlock")):
         mod = sys.modules.get(modname)
-        if mod is not None and hasattr(mod, "MambaBlock"):
-            blocks.append(mod.MambaBlock)
+        if mod is not None and hasattr(mod, cls):
+            blocks.append(getattr(mod, cls))
     for i, blk in enumerate(blocks):
         for name in _BLOCK_METHODS:
             # the ONNX variant's step() has another signature; only same-signature methods move
@@ -69,9 +69,9 @@ def install(fuse_block: bool = False) -> None:
             if norm is not None:
                 _swap(norm, "forward", _m.rmsnorm_forward)
         vim = sys.modules.get("mambapy.vim")
-        if vim is not None and hasattr(vim, "MambaBlock"):
+        if vim is not None and hasattr(vim, "VMambaBlock"):
             # the bidirectional block: second direction scanned right-to-left inside the kernels
-            _swap(vim.MambaBlock, "forward", _v.forward)
+            _swap(vim.VMambaBlock, "forward", _v.forward)
 
 
 def uninstall() -> None:

@@ -126,9 +126,10 @@ def test_vim_bidirectional_block(ref, fuse_block):
     x, gy = torch.randn(2, 48, 32), torch.randn(2, 48, 32)
     want = _fwd_bwd(cpu, x, gy)
     mamba_b200.install(fuse_block=fuse_block)
+    assert rv.VMambaBlock.selective_scan is mamba_b200.selective_scan        # the scan itself is always swapped
     if fuse_block:
         from mamba_b200 import vim as kernel_vim
-        assert rv.MambaBlock.forward is kernel_vim.forward
+        assert rv.VMambaBlock.forward is kernel_vim.forward
     got = _fwd_bwd(gpu, x.to(DEV), gy.to(DEV))
     _check(got, want, f"vim fuse_block={fuse_block}")
 
