@@ -78,27 +78,6 @@ __device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
   asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
 }
 
-// Sum of two values per lane over groups of lanes on the tensor core: one m16n8k8 TF32 MMA with a 0/1
-// selection matrix as A and the lanes' values as B.  With b0, b1 the values of lane l, the lane gets back
-//   s0 = sum of b0 over the 8 lanes {8j .. 8j+7} whose (l & 3) equals j... precisely: over the lanes of the
-//        two 4-lane groups 2*(l & 3) and 2*(l & 3) + 1, i.e. lanes 8*(l & 3) .. 8*(l & 3) + 7,
-//   s1 = the same for b1,
-// replicated in every group of four lanes.  The operands are read as TF32 (the low 13 mantissa bits are
-// ignored), the sum is float32; used only where the result is rounded to bfloat16 anyway.  Nothing goes
-// through shared memory.
-__device__ __forceinline__ void mma_sum_over_8_lanes(float b0, float b1, float& s0, float& s1) {
-  float c0, c1, c2, c3;
-  const uint32_t one = 0x3f800000u, zero = 0u;
-  asm volatile(
-      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
-      "{%10, %11, %12, %13};"
-      : "=f"(c0), "=f"(c1), "=f"(c2), "=f"(c3)
-      : "r"(one), "r"(zero), "r"(zero), "r"(one), "r"(__float_as_uint(b0)), "r"(__float_as_uint(b1)), "f"(0.f),
-        "f"(0.f), "f"(0.f), "f"(0.f));
-  s0 = c0 + c1;
-  s1 = c2 + c3;
-}
-
 // The softplus option and the presence of the gate are template parameters too: as run-time flags they
 // cost the converter and finishing warps (the busiest ones) branches and selects, 6 % of the launch.
 template <typename T, bool kRev, bool kSoftplus, bool kHasZ>
@@ -107,10 +86,6 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
   using S = TmaBwdSmem<T>;
   constexpr int kStages = S::kStages, kAhead = S::kStages - 2;
   constexpr int N = kBN;
-  // bf16 I/O: the dB, dC products are summed over the 8 channels of a recurrence warp by the tensor core
-  // (registers in, registers out) instead of going through shared memory one product at a time; float32
-  // I/O keeps the exact shared-memory reduction (TF32 operands would cost it its 1e-4 contract).
-  constexpr bool kMma = sizeof(T) == 2;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
   float2* s_op = reinterpret_cast<float2*>(smem_raw + S::kOp);
@@ -171,10 +146,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
   }
   if (warp < 4) {
     // ================================================================== consumers
-    // lane -> (channel, state quad).  The MMA sums over lanes 8j .. 8j+7, so there the 8 channels of the
-    // warp sit on the low lane bits and the quad on the high ones.
-    const int e_l = kMma ? warp * 8 + (lane & 7) : tid >> 2;
-    const int q = kMma ? lane >> 3 : tid & 3;
+    const int e_l = tid >> 2, q = tid & 3;
     const int64_t e = e0 + e_l;
     const bool e_ok = e < p.ED;
     float2 A2[2], gc[2], dAacc[2];
@@ -260,8 +232,7 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
           const int64_t wseq = j * kWinsPerTile + (1 - half) * (kHalf / kBWin) + (kHalf / kBWin - 1 - wi);
           const int wb = int(wseq & 1);
           // asked now, needed only before the first store of the window
-          bool slot_free = wseq < 2 || mbar_test(&win_empty[wb], int(((wseq - 2) >> 1) & 1));
-          if constexpr (kMma) slot_free = __all_sync(0xffffffffu, slot_free);   // the MMA needs the warp converged
+          const bool slot_free = wseq < 2 || mbar_test(&win_empty[wb], int(((wseq - 2) >> 1) & 1));
           float* np = s_np + wb * kBWin * 3 * 128;
           float4* ep = s_ep + wb * kBWin * 2 * 4 * kEpStride;
 #pragma unroll
@@ -298,22 +269,8 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
             np[(ti * 3 + 0) * 128 + npo] = ysum.x + ysum.y;
             np[(ti * 3 + 1) * 128 + npo] = gBs.x + gBs.y;
             np[(ti * 3 + 2) * 128 + npo] = wAs.x + wAs.y;
-            if constexpr (kMma) {
-              // sums over this warp's 8 channels; lane l receives those of state quad l & 3.  Every 4-lane group
-              // holds the same sums: lanes 0-3 store them, as {dB[n], dC[n]} pairs, n = 4 * lane + j.
-              float2* ep2 = reinterpret_cast<float2*>(ep) + ((ti * 4 + warp) * 4 + (lane & 3)) * 4;
-              const float pb[4] = {dBp[0].x, dBp[0].y, dBp[1].x, dBp[1].y};
-              const float pc[4] = {dCp[0].x, dCp[0].y, dCp[1].x, dCp[1].y};
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float sb, sc;
-                mma_sum_over_8_lanes(pb[j], pc[j], sb, sc);
-                if (lane < 4) ep2[j] = make_float2(sb, sc);
-              }
-            } else {
-              ep[((ti * 2 + 0) * 4 + q) * kEpStride + e_l] = make_float4(dBp[0].x, dBp[0].y, dBp[1].x, dBp[1].y);
-              ep[((ti * 2 + 1) * 4 + q) * kEpStride + e_l] = make_float4(dCp[0].x, dCp[0].y, dCp[1].x, dCp[1].y);
-            }
+            ep[((ti * 2 + 0) * 4 + q) * kEpStride + e_l] = make_float4(dBp[0].x, dBp[0].y, dBp[1].x, dBp[1].y);
+            ep[((ti * 2 + 1) * 4 + q) * kEpStride + e_l] = make_float4(dCp[0].x, dCp[0].y, dCp[1].x, dCp[1].y);
           }
           mbar_arrive(&win_full[wb]);
         }
@@ -421,30 +378,6 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
 
   if (warp == 6) {
     // ================================================================== dB, dC: sums over channels
-    if constexpr (kMma) {
-      // the recurrence warps left {dB[n], dC[n]} summed over their 8 channels: add the 4 warps, one n per lane
-      const int ti = lane >> 4, n = lane & 15;
-      float* gB = p.dB + b * p.L * N + n;
-      float* gC = p.dC + b * p.L * N + n;
-      for (int64_t j = 0; j < ntiles; ++j) {
-        const int64_t t0 = tile_t0(j);
-#pragma unroll 1
-        for (int wl = 0; wl < kWinsPerTile; ++wl) {
-          const int64_t wseq = j * kWinsPerTile + wl;
-          const int wb = int(wseq & 1);
-          if (!mbar_wait(&win_full[wb], int((wseq >> 1) & 1))) { fail(); return; }
-          const float2* src = reinterpret_cast<const float2*>(s_ep + wb * kBWin * 2 * 4 * kEpStride) + ti * 4 * 16 + n;
-          const float2 v0 = src[0], v1 = src[16], v2 = src[32], v3 = src[48];
-          mbar_arrive(&win_empty[wb]);
-          const int64_t t = t0 + row(win_t(wl) + ti);
-          if (t < p.L) {
-            atomicAdd(gB + t * N, (v0.x + v1.x) + (v2.x + v3.x));
-            atomicAdd(gC + t * N, (v0.y + v1.y) + (v2.y + v3.y));
-          }
-        }
-      }
-      return;
-    }
     const int ti = lane >> 4, which = (lane >> 3) & 1, qq = (lane >> 1) & 3, hf = lane & 1;
     float* gbase = (which ? p.dC : p.dB) + b * p.L * N + 4 * qq + 2 * hf;
     for (int64_t j = 0; j < ntiles; ++j) {
