@@ -119,6 +119,9 @@ __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
 // Producer and consumer warps of one CTA hand tiles to each other through these.  A wait
 // that does not complete within kSpinLimit polls gives up and reports it; nothing spins
 // without a limit.
+#ifndef MB200_POLL_NS
+#define MB200_POLL_NS 100
+#endif
 constexpr int kSpinLimit = 1 << 22;          // polls at least 100 ns apart: gives up after roughly a second
 enum { MB200_DEV_OK = 0, MB200_DEV_WAIT_TIMEOUT = 1 };
 
@@ -164,7 +167,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, int parity) {
   const uint32_t addr = smem_u32(bar);
   if (mbar_poll(addr, parity)) return true;
   for (int i = 0; i < kSpinLimit; ++i) {
-    __nanosleep(100);
+    if (MB200_POLL_NS > 0) __nanosleep(MB200_POLL_NS);
     if (mbar_poll(addr, parity)) return true;
   }
   return false;

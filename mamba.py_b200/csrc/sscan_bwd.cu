@@ -74,8 +74,8 @@ template <typename T> struct TmaBwdSmem {
 // XOR keeps the finishing warps' loads (channels 2l, 2l+1 per lane) free of bank conflicts.
 __device__ __forceinline__ int np_chan(int c) { return c ^ ((c >> 3) & 1); }
 
-__device__ __forceinline__ void red_add_v2(float* addr, float a, float b) {
-  asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(addr), "f"(a), "f"(b) : "memory");
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
 
 // The softplus option and the presence of the gate are template parameters too: as run-time flags they
@@ -378,28 +378,35 @@ sscan_bwd_tma_kernel(const __grid_constant__ BwdMaps maps, const SscanBwdParams 
 
   if (warp == 6) {
     // ================================================================== dB, dC: sums over channels
-    const int ti = lane >> 4, which = (lane >> 3) & 1, qq = (lane >> 1) & 3, hf = lane & 1;
-    float* gbase = (which ? p.dC : p.dB) + b * p.L * N + 4 * qq + 2 * hf;
-    for (int64_t j = 0; j < ntiles; ++j) {
+    // A lane owns one row of products (timestep of the window, dB | dC, state quad: 16 rows) and one half
+    // of the CTA's 32 channels; it adds its 16 float4 and sends the four sums to global memory with one
+    // vector atomic.  Rows are kEpStride = 34 float4 apart, which puts rows r and r + 4 into the same
+    // banks: the lanes of rows 4..7 and 12..15 therefore take each pair of neighbouring channels in the
+    // opposite order (index c ^ 1), through two base pointers, so that no index is computed in the loop.
+    const int hf = lane >> 4, r = lane & 15;
+    const int ti = r >> 3, which = (r >> 2) & 1, qq = r & 3;       // r = (ti * 2 + which) * 4 + qq
+    float* gbase = (which ? p.dC : p.dB) + b * p.L * N + 4 * qq;
+    const int nt = int(ntiles);
+    for (int j = 0; j < nt; ++j) {
       const int64_t t0 = tile_t0(j);
 #pragma unroll 1
       for (int wl = 0; wl < kWinsPerTile; ++wl) {
-        const int64_t wseq = j * kWinsPerTile + wl;
-        const int wb = int(wseq & 1);
-        if (!mbar_wait(&win_full[wb], int((wseq >> 1) & 1))) { fail(); return; }
-        const float* src = reinterpret_cast<const float*>(
-                               s_ep + wb * kBWin * 2 * 4 * kEpStride + ((ti * 2 + which) * 4 + qq) * kEpStride) + 2 * hf;
+        const int wseq = j * kWinsPerTile + wl;
+        const int wb = wseq & 1;
+        if (!mbar_wait(&win_full[wb], (wseq >> 1) & 1)) { fail(); return; }
+        const float4* rowp = s_ep + wb * kBWin * 2 * 4 * kEpStride + r * kEpStride + hf * 16;
+        const float4* pe = rowp + which;                          // even channels: c ^ which = c + which
+        const float4* po = rowp - which;                          // odd channels:  c ^ which = c - which
         float2 acc0 = make_float2(0.f, 0.f), acc1 = acc0;
-        // lanes of the dC rows start one channel later than those of the dB rows: with 8 banks between
-        // consecutive rows this spreads a half-warp's 16 loads over all 32 banks
 #pragma unroll
-        for (int k = 0; k < kBTE; k += 2) {
-          acc0 = __fadd2_rn(acc0, *reinterpret_cast<const float2*>(src + 4 * ((k + which) & (kBTE - 1))));
-          acc1 = __fadd2_rn(acc1, *reinterpret_cast<const float2*>(src + 4 * ((k + 1 + which) & (kBTE - 1))));
+        for (int c = 0; c < kBTE / 2; ++c) {
+          const float4 v = (c & 1) ? po[c] : pe[c];
+          acc0 = __fadd2_rn(acc0, make_float2(v.x, v.y));
+          acc1 = __fadd2_rn(acc1, make_float2(v.z, v.w));
         }
         mbar_arrive(&win_empty[wb]);
         const int64_t t = t0 + row(win_t(wl) + ti);
-        if (t < p.L) red_add_v2(gbase + t * N, acc0.x + acc1.x, acc0.y + acc1.y);
+        if (t < p.L) red_add_v4(gbase + t * N, acc0.x, acc0.y, acc1.x, acc1.y);
       }
     }
     return;

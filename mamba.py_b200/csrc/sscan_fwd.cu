@@ -65,7 +65,7 @@ template <int N> struct FwdGeom {
   static constexpr int kLPE = N / 4;                                   // lanes per channel group
   static constexpr int kConsumers = 32 * kCW;
   static constexpr int kProducers = 32 * kPW;
-  static constexpr int kThreads = kConsumers + kProducers;
+  static constexpr int kThreads = kConsumers + kProducers + 32;      // + the warp that issues the TMA copies
   static constexpr int kTE = kConsumers / kLPE * kCPT;                 // channels per CTA
   static_assert(kCPT == 1 || (kCPT == 2 && N == 16), "two channels per thread are laid out for d_state 16");
   static_assert(kTE % 8 == 0, "a tile row is a whole number of 16-byte vectors in bf16");
@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(FwdGeom<N>::kThreads, FwdGeom<N>::kOcc)
 sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams p) {
   using G = FwdGeom<N>;
   using S = TmaFwdSmem<T, N>;
-  constexpr int kLPE = G::kLPE, kTE = G::kTE, kStages = S::kStages, kAhead = S::kStages - 2;
+  constexpr int kLPE = G::kLPE, kTE = G::kTE, kStages = S::kStages;
   constexpr int kCPT = G::kCPT, kNC = G::kConsumers, kNP = G::kProducers, kYpRow = S::kYpRow;
 
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -300,22 +300,20 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
           *reinterpret_cast<float4*>(p.hT + (b * p.ED + e0 + e_l + i) * N + 4 * q) =
               make_float4(hlo[i].x, hlo[i].y, hhi[i].x, hhi[i].y);
     }
-  } else {
-    // ------------------------------------------------------------------ producers
-    const int pt = tid - kNC;
-    constexpr int kVecs = kTile * kTE / 4;                 // 4-channel vectors per activation tile
-    constexpr int kVecPerRow = kTE / 4;
-    T* gy = has_y ? static_cast<T*>(p.y) + b * p.y_sb + e0 : nullptr;
+  } else if (tid >= kNC + kNP) {
+    // ------------------------------------------------------------------ loader
+    // One lane issues the TMA copies, as far ahead as the ring has free stages.  Issuing the five copies of
+    // a tile takes the issuing thread over a thousand cycles (clock64 stamps); done by a producer thread,
+    // as it used to be, that made its warp the last one to hand every tile to the recurrence warps.
+    if (tid != kNC + kNP) return;
     const uint32_t stage_tx = uint32_t((has_z ? 3 : 2) * S::kActBytes + 2 * S::kBcBytes);
-
-    auto stage_ptr = [&](int64_t kt) { return smem_raw + S::kRaw + int(kt % kStages) * S::kStageBytes; };
-    auto fail = [&]() { atomicExch(&g_fwd_status, MB200_DEV_WAIT_TIMEOUT); };
-
-    // one thread: start the copies of tile kt into its ring stage
-    auto issue = [&](int64_t kt) -> bool {
+    for (int64_t kt = 0; kt < ntiles; ++kt) {
       const int r = int(kt % kStages);
-      if (kt >= kStages && !mbar_wait(&raw_free[r], int((kt / kStages - 1) & 1))) return false;
-      unsigned char* st = stage_ptr(kt);
+      if (kt >= kStages && !mbar_wait(&raw_free[r], int((kt / kStages - 1) & 1))) {
+        atomicExch(&g_fwd_status, MB200_DEV_WAIT_TIMEOUT);
+        return;
+      }
+      unsigned char* st = smem_raw + S::kRaw + r * S::kStageBytes;
       const int t0 = int(tile_t0(kt));
       mbar_expect_tx(&raw_full[r], stage_tx);
       tma_load_3d(st, &maps.x, int(e0), t0, int(b), &raw_full[r]);
@@ -323,8 +321,17 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
       if (has_z) tma_load_3d(st + 2 * S::kActBytes, &maps.z, int(e0), t0, int(b), &raw_full[r]);
       tma_load_3d(st + 3 * S::kActBytes, &maps.B, 0, t0, int(b), &raw_full[r]);
       tma_load_3d(st + 3 * S::kActBytes + S::kBcBytes, &maps.C, 0, t0, int(b), &raw_full[r]);
-      return true;
-    };
+    }
+  } else {
+    // ------------------------------------------------------------------ producers
+    const int pt = tid - kNC;
+    constexpr int kVecs = kTile * kTE / 4;                 // 4-channel vectors per activation tile
+    constexpr int kVecPerRow = kTE / 4;
+    T* gy = has_y ? static_cast<T*>(p.y) + b * p.y_sb + e0 : nullptr;
+
+    auto stage_ptr = [&](int64_t kt) { return smem_raw + S::kRaw + int(kt % kStages) * S::kStageBytes; };
+    auto fail = [&]() { atomicExch(&g_fwd_status, MB200_DEV_WAIT_TIMEOUT); };
+
     // raw tile kt -> float32 operands in buffer kt & 1
     auto convert = [&](int64_t kt) {
       const int buf = int(kt & 1);
@@ -426,10 +433,6 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
       }
     };
 
-    if (pt == 0) {
-      for (int64_t kt = 0; kt < kAhead && kt < ntiles; ++kt)
-        if (!issue(kt)) { fail(); return; }
-    }
     for (int64_t kt = 0; kt < ntiles; ++kt) {
       if (kt >= 2) {
         if (!mbar_wait(&op_empty[kt & 1], int(((kt - 2) >> 1) & 1))) { fail(); return; }
@@ -439,7 +442,6 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
       if (!mbar_wait(&raw_full[kt % kStages], int((kt / kStages) & 1))) { fail(); return; }
       convert(kt);
       mbar_arrive(&op_full[kt & 1]);
-      if (pt == 0 && kt + kAhead < ntiles && !issue(kt + kAhead)) { fail(); return; }
     }
     for (int64_t kt = ntiles >= 2 ? ntiles - 2 : 0; kt < ntiles; ++kt) {
       if (!mbar_wait(&op_empty[kt & 1], int((kt >> 1) & 1))) { fail(); return; }
