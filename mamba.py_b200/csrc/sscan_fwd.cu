@@ -57,6 +57,20 @@ constexpr int kTile = 2 * kChunk;          // timesteps per tile (two saved stat
 #ifndef MB200_FWD_OCC
 #define MB200_FWD_OCC 3
 #endif
+#ifndef MB200_FWD_PIPE
+#define MB200_FWD_PIPE 1
+#endif
+#ifndef MB200_FWD_DEFER
+#define MB200_FWD_DEFER 1
+#endif
+#ifndef MB200_FWD_LA
+#define MB200_FWD_LA 2
+#endif
+#ifndef MB200_FWD_EA
+#define MB200_FWD_EA 1
+#endif
+constexpr int kLoadAhead = MB200_FWD_LA, kDecayAhead = MB200_FWD_EA;   // software-pipeline depths of the recurrence warps
+constexpr int kDefer = MB200_FWD_DEFER;     // timesteps of partial sums a recurrence thread holds before storing them
 template <int N> struct FwdGeom {
   static constexpr int kCPT = (N == 16) ? MB200_FWD_CPT : 1;
   static constexpr int kCW = (N == 16) ? MB200_FWD_CW : 4;
@@ -237,6 +251,96 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
         const float* sB = s_B + buf * kTile * N + 4 * q;
         const float* sC = s_C + buf * kTile * N + 4 * q;
         float* yp = s_yp + buf * kTile * kYpRow;
+#if MB200_FWD_PIPE
+        float ypend[kTile][kCPT];                                            // partial sums not stored yet
+        // One timestep is three stages -- operand loads, decays and inputs (ex2), recurrence and contraction --
+        // and only the last one depends on the previous timestep.  The stages of three consecutive timesteps
+        // are written side by side (loads of t+2, decays of t+1, recurrence of t), so that this in-order warp
+        // always has independent work between an instruction and the first use of its result.
+        struct Loaded { float2 o[kCPT]; float4 Bq, Cq; };
+        struct Ready { float2 a_lo[kCPT], a_hi[kCPT], dxx[kCPT]; float4 Bq, Cq; };
+        auto load = [&](int t) {
+          Loaded l;
+          const int r = rb0 + t * rstep;
+          if constexpr (kCPT == 1) {
+            l.o[0] = op[r * kTE + ((t & 1) ? off_odd : off_even)];
+          } else {
+            const float4 o4 = *reinterpret_cast<const float4*>(op + r * kTE + ((t & 1) ? off_odd : off_even));
+            l.o[0] = make_float2(o4.x, o4.y); l.o[1] = make_float2(o4.z, o4.w);
+          }
+          l.Bq = *reinterpret_cast<const float4*>(sB + r * N);
+          l.Cq = l.Bq;
+          if constexpr (kHasY) l.Cq = *reinterpret_cast<const float4*>(sC + r * N);
+          return l;
+        };
+        auto prepare = [&](const Loaded& l) {
+          Ready e;
+#pragma unroll
+          for (int i = 0; i < kCPT; ++i) {
+            e.dxx[i] = make_float2(l.o[i].y, l.o[i].y);
+            decay4<kStruct>(l.o[i].x, A2lo[i], A2hi[i], A0[i], e.a_lo[i], e.a_hi[i]);
+          }
+          e.Bq = l.Bq; e.Cq = l.Cq;
+          return e;
+        };
+        Loaded ld[kTile];
+        Ready rd[kTile];
+#pragma unroll
+        for (int t = 0; t < kLoadAhead; ++t) ld[t] = load(t);
+#pragma unroll
+        for (int t = 0; t < kDecayAhead; ++t) rd[t] = prepare(ld[t]);
+#pragma unroll
+        for (int t = 0; t < kTile; ++t) {
+          if (t % kChunk == 0 && carry_base) {                              // state entering this chunk
+            const int64_t c = t0a / kChunk + (rev ? 1 - t / kChunk : t / kChunk);
+            if (c < nchunks) {
+#pragma unroll
+              for (int i = 0; i < kCPT; ++i)
+                if (e_ok[i])
+                  *reinterpret_cast<float4*>(carry_base + (c * p.ED + i) * N) =
+                      make_float4(hlo[i].x, hlo[i].y, hhi[i].x, hhi[i].y);
+            }
+          }
+          if (t + kLoadAhead < kTile) ld[t + kLoadAhead] = load(t + kLoadAhead);
+          if (t + kDecayAhead < kTile) rd[t + kDecayAhead] = prepare(ld[t + kDecayAhead]);
+          const Ready cur = rd[t];
+          const float4 Bq = cur.Bq, Cq = cur.Cq;
+          float ysum[kCPT];
+#pragma unroll
+          for (int i = 0; i < kCPT; ++i) {
+            const float2 dxx = cur.dxx[i], a_lo = cur.a_lo[i], a_hi = cur.a_hi[i];
+            if constexpr (kCarry) {
+              hlo[i] = __fmul2_rn(a_lo, __ffma2_rn(dxx, make_float2(Bq.x, Bq.y), hlo[i]));
+              hhi[i] = __fmul2_rn(a_hi, __ffma2_rn(dxx, make_float2(Bq.z, Bq.w), hhi[i]));
+            } else {
+              const float2 u_lo = __fmul2_rn(dxx, make_float2(Bq.x, Bq.y));
+              const float2 u_hi = __fmul2_rn(dxx, make_float2(Bq.z, Bq.w));
+              hlo[i] = __ffma2_rn(a_lo, hlo[i], u_lo);
+              hhi[i] = __ffma2_rn(a_hi, hhi[i], u_hi);
+              if constexpr (kHasY) {
+                float2 acc = __fmul2_rn(hlo[i], make_float2(Cq.x, Cq.y));
+                acc = __ffma2_rn(hhi[i], make_float2(Cq.z, Cq.w), acc);
+                ysum[i] = acc.x + acc.y;
+              }
+            }
+          }
+          if constexpr (kHasY && !kCarry) {
+            // A shared-memory store between two timesteps' operand loads pins the loads behind it (the
+            // compiler cannot tell that they do not alias); the partial sums are therefore held in
+            // registers and stored kDefer timesteps at a time.
+#pragma unroll
+            for (int i = 0; i < kCPT; ++i) ypend[t][i] = ysum[i];
+            if ((t + 1) % kDefer == 0) {
+#pragma unroll
+              for (int u = t + 1 - kDefer; u <= t; ++u) {
+                float* dst = yp + u * kYpRow + ((u & 1) ? yp_off1 : yp_off0);
+                if constexpr (kCPT == 1) *dst = ypend[u][0];
+                else *reinterpret_cast<float2*>(dst) = make_float2(ypend[u][0], ypend[u][1]);
+              }
+            }
+          }
+        }
+#else
 #pragma unroll
         for (int t = 0; t < kTile; ++t) {
           if (t % kChunk == 0 && carry_base) {                              // state entering this chunk
@@ -287,6 +391,7 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
             else *reinterpret_cast<float2*>(dst) = make_float2(ysum[0], ysum[1]);
           }
         }
+#endif
         mbar_arrive(&op_empty[buf]);
       }
       return true;
