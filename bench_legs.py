@@ -164,11 +164,11 @@ def bench_decode(args, rank, world, dev, T, summary=False):
 
 # ---------------------------------------------------------------------------- sequence sharding
 def _lshard_pass_times(step, n):
-    """Run `step` n times with every shard-local pass (methods of lshard.CudaOps) and every collective
+    """Run `step` n times with every shard-local pass (methods of split.CudaOps) and every collective
     of the sequence-sharded scan bracketed by its own CUDA events.  Returns ({pass: ms per step},
     ms per step spent in collectives); this rank's numbers, taken outside the timed regions."""
     import torch.distributed as dist
-    from mamba_b200 import lshard
+    from mamba_b200 import split
     rec = []
 
     def timed(name, fn):
@@ -182,12 +182,12 @@ def _lshard_pass_times(step, n):
         return wrapped
 
     saved = []
-    for name, attr in list(vars(lshard.CudaOps).items()):
+    for name, attr in list(vars(split.CudaOps).items()):
         if isinstance(attr, staticmethod):
-            saved.append((lshard.CudaOps, name, attr))
-            setattr(lshard.CudaOps, name, staticmethod(timed(name, attr.__func__)))
-    saved.append((lshard, "_gather", lshard._gather))
-    lshard._gather = timed("all_gather", lshard._gather)
+            saved.append((split.CudaOps, name, attr))
+            setattr(split.CudaOps, name, staticmethod(timed(name, attr.__func__)))
+    saved.append((split, "_gather", split._gather))
+    split._gather = timed("all_gather", split._gather)
     saved.append((dist, "all_reduce", dist.all_reduce))
     dist.all_reduce = timed("all_reduce", dist.all_reduce)
     try:

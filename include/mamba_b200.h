@@ -248,6 +248,26 @@ int mb200_conv1d_silu_bwd(const void* x, const float* w, const float* bias, cons
 int mb200_carry_fold(const float* P, const float* S, float* out,
                      int64_t R, int64_t M, int rank, int reverse, void* stream);
 
+/* The same fold for a RANGE of pieces, and for `batch` independent sequences, in one launch (no reference
+ * counterpart).  P, S: (batch, R, M); init: (batch, M) or NULL; out: (batch, num, M).  out[bb][i - first] is
+ * the state entering piece i of sequence bb (reverse == 0: fold of pieces 0..i-1 in order, starting from
+ * init[bb] or from 0) or the gradient carry entering piece i from the right (reverse == 1: fold of pieces
+ * R-1..i+1, starting from init[bb] or 0), for i = first .. first+num-1.  Used when a device cuts its span
+ * into several pieces that are scanned side by side as extra batch rows. */
+int mb200_carry_fold_range(const float* P, const float* S, const float* init, float* out, int64_t batch,
+                           int64_t R, int64_t M, int first, int num, int reverse, void* stream);
+
+/* ---- Forward carry pass of a split sequence (no reference counterpart): for every batch row, the state
+ * h_out (B, ED, N) the span reaches from a ZERO state and the span's decay product
+ * p_out[b,e,n] = exp(A[e,n] * sum_t delta[b,t,e]), from one pass over x, delta, Bm (same layouts and
+ * softplus option as mb200_sscan_fwd; no y, no C, no saved states).  Together with mb200_carry_fold[_range]
+ * these give the state entering every piece.  MB200_REVERSE is not served here. */
+int mb200_sscan_fwd_carry(const void* x, const void* delta, const float* A, const void* Bm,
+                          const float* delta_bias, float* h_out, float* p_out,
+                          int64_t B, int64_t L, int64_t ED, int N,
+                          int64_t x_sb, int64_t x_sl, int64_t d_sb, int64_t d_sl,
+                          int64_t b_sb, int64_t b_sl, int dtype, int flags, void* stream);
+
 /* ---- Decay product of a shard: P[b,e,n] = exp(A[e,n] * sum_t delta[b,t,e]) (with the same
  * softplus option as the scan).  Used with mb200_carry_fold by the sequence-sharded scan. */
 int mb200_decay_prod(const void* delta, const float* A, const float* delta_bias, float* P,

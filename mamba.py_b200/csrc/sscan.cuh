@@ -88,6 +88,7 @@ struct SscanFwdParams {
   const float *A, *D, *delta_bias, *h0;
   void* y;
   float *hT, *carries;
+  float* pT = nullptr;         // (B, ED, N) decay product of the whole span; written by the state-only pass
   int64_t B, L, ED;
   int64_t x_sb, x_sl, d_sb, d_sl, z_sb, z_sl, b_sb, b_sl, c_sb, c_sl, y_sb, y_sl;
   int flags;

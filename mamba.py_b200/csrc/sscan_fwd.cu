@@ -57,9 +57,6 @@ constexpr int kTile = 2 * kChunk;          // timesteps per tile (two saved stat
 #ifndef MB200_FWD_OCC
 #define MB200_FWD_OCC 3
 #endif
-#ifndef MB200_FWD_PIPE
-#define MB200_FWD_PIPE 1
-#endif
 #ifndef MB200_FWD_DEFER
 #define MB200_FWD_DEFER 1
 #endif
@@ -238,6 +235,13 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
     constexpr int rb0 = rev ? kTile - 1 : 0, rstep = rev ? -1 : 1;
     const int off_even = rev ? op_off1 : op_off0, off_odd = rev ? op_off0 : op_off1;
 
+    // The pass that only wants states (the carry pass of a split sequence) also returns the decay product of
+    // the whole span, exp(A * sum_t delta[t]): the sum costs one add per timestep here, and a pass of its own
+    // over delta otherwise.
+    constexpr bool kWantP = !kHasY && !kCarry;
+    float dsum[kCPT], dcomp[kCPT];
+#pragma unroll
+    for (int i = 0; i < kCPT; ++i) dsum[i] = dcomp[i] = 0.f;
     auto run_tiles = [&](auto struct_tag) {
       constexpr bool kStruct = decltype(struct_tag)::value;
       for (int64_t kt = 0; kt < ntiles; ++kt) {
@@ -251,7 +255,6 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
         const float* sB = s_B + buf * kTile * N + 4 * q;
         const float* sC = s_C + buf * kTile * N + 4 * q;
         float* yp = s_yp + buf * kTile * kYpRow;
-#if MB200_FWD_PIPE
         float ypend[kTile][kCPT];                                            // partial sums not stored yet
         // One timestep is three stages -- operand loads, decays and inputs (ex2), recurrence and contraction --
         // and only the last one depends on the previous timestep.  The stages of three consecutive timesteps
@@ -285,6 +288,9 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
         };
         Loaded ld[kTile];
         Ready rd[kTile];
+        float dtile[kCPT];                                                   // sum of delta over this tile
+#pragma unroll
+        for (int i = 0; i < kCPT; ++i) dtile[i] = 0.f;
 #pragma unroll
         for (int t = 0; t < kLoadAhead; ++t) ld[t] = load(t);
 #pragma unroll
@@ -304,6 +310,10 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
           if (t + kLoadAhead < kTile) ld[t + kLoadAhead] = load(t + kLoadAhead);
           if (t + kDecayAhead < kTile) rd[t + kDecayAhead] = prepare(ld[t + kDecayAhead]);
           const Ready cur = rd[t];
+          if constexpr (kWantP) {
+#pragma unroll
+            for (int i = 0; i < kCPT; ++i) dtile[i] += ld[t].o[i].x;
+          }
           const float4 Bq = cur.Bq, Cq = cur.Cq;
           float ysum[kCPT];
 #pragma unroll
@@ -340,58 +350,15 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
             }
           }
         }
-#else
-#pragma unroll
-        for (int t = 0; t < kTile; ++t) {
-          if (t % kChunk == 0 && carry_base) {                              // state entering this chunk
-            const int64_t c = t0a / kChunk + (rev ? 1 - t / kChunk : t / kChunk);
-            if (c < nchunks) {
-#pragma unroll
-              for (int i = 0; i < kCPT; ++i)
-                if (e_ok[i])
-                  *reinterpret_cast<float4*>(carry_base + (c * p.ED + i) * N) =
-                      make_float4(hlo[i].x, hlo[i].y, hhi[i].x, hhi[i].y);
-            }
-          }
-          const int r = rb0 + t * rstep;
-          float2 o[kCPT];                                                    // {delta, delta*x} per channel
-          if constexpr (kCPT == 1) {
-            o[0] = op[r * kTE + ((t & 1) ? off_odd : off_even)];
-          } else {
-            const float4 o4 = *reinterpret_cast<const float4*>(op + r * kTE + ((t & 1) ? off_odd : off_even));
-            o[0] = make_float2(o4.x, o4.y); o[1] = make_float2(o4.z, o4.w);
-          }
-          const float4 Bq = *reinterpret_cast<const float4*>(sB + r * N);
-          float4 Cq = Bq;
-          if constexpr (kHasY) Cq = *reinterpret_cast<const float4*>(sC + r * N);
-          float ysum[kCPT];
+        if constexpr (kWantP) {                     // compensated sum over the tiles: L can be 10^5 and it feeds an exponent
 #pragma unroll
           for (int i = 0; i < kCPT; ++i) {
-            const float2 dxx = make_float2(o[i].y, o[i].y);
-            float2 a_lo, a_hi;
-            decay4<kStruct>(o[i].x, A2lo[i], A2hi[i], A0[i], a_lo, a_hi);
-            if constexpr (kCarry) {
-              hlo[i] = __fmul2_rn(a_lo, __ffma2_rn(dxx, make_float2(Bq.x, Bq.y), hlo[i]));
-              hhi[i] = __fmul2_rn(a_hi, __ffma2_rn(dxx, make_float2(Bq.z, Bq.w), hhi[i]));
-            } else {
-              const float2 u_lo = __fmul2_rn(dxx, make_float2(Bq.x, Bq.y));
-              const float2 u_hi = __fmul2_rn(dxx, make_float2(Bq.z, Bq.w));
-              hlo[i] = __ffma2_rn(a_lo, hlo[i], u_lo);
-              hhi[i] = __ffma2_rn(a_hi, hhi[i], u_hi);
-              if constexpr (kHasY) {
-                float2 acc = __fmul2_rn(hlo[i], make_float2(Cq.x, Cq.y));
-                acc = __ffma2_rn(hhi[i], make_float2(Cq.z, Cq.w), acc);
-                ysum[i] = acc.x + acc.y;
-              }
-            }
-          }
-          if constexpr (kHasY && !kCarry) {
-            float* dst = yp + t * kYpRow + ((t & 1) ? yp_off1 : yp_off0);
-            if constexpr (kCPT == 1) *dst = ysum[0];
-            else *reinterpret_cast<float2*>(dst) = make_float2(ysum[0], ysum[1]);
+            const float yk = dtile[i] - dcomp[i];
+            const float tk = dsum[i] + yk;
+            dcomp[i] = (tk - dsum[i]) - yk;
+            dsum[i] = tk;
           }
         }
-#endif
         mbar_arrive(&op_empty[buf]);
       }
       return true;
@@ -404,6 +371,16 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
         if (e_ok[i])
           *reinterpret_cast<float4*>(p.hT + (b * p.ED + e0 + e_l + i) * N + 4 * q) =
               make_float4(hlo[i].x, hlo[i].y, hhi[i].x, hhi[i].y);
+    }
+    if constexpr (kWantP) {
+      if (p.pT) {
+#pragma unroll
+        for (int i = 0; i < kCPT; ++i)
+          if (e_ok[i])
+            *reinterpret_cast<float4*>(p.pT + (b * p.ED + e0 + e_l + i) * N + 4 * q) =
+                make_float4(ex2f(A2lo[i].x * dsum[i]), ex2f(A2lo[i].y * dsum[i]), ex2f(A2hi[i].x * dsum[i]),
+                            ex2f(A2hi[i].y * dsum[i]));
+      }
     }
   } else if (tid >= kNC + kNP) {
     // ------------------------------------------------------------------ loader
@@ -653,7 +630,7 @@ extern "C" int mb200_sscan_fwd(const void* x, const void* delta, const void* z, 
   if (!aligned16(h0) || !aligned16(hT) || !aligned16(carries)) return MB200_EALIGN;
   SscanFwdParams p;
   p.x = x; p.delta = delta; p.z = z; p.A = A; p.Bm = Bm; p.Cm = Cm; p.D = D;
-  p.delta_bias = delta_bias; p.h0 = h0; p.y = y; p.hT = hT; p.carries = carries;
+  p.delta_bias = delta_bias; p.h0 = h0; p.y = y; p.hT = hT; p.pT = nullptr; p.carries = carries;
   p.B = B; p.L = L; p.ED = ED;
   p.x_sb = x_sb; p.x_sl = x_sl; p.d_sb = d_sb; p.d_sl = d_sl; p.z_sb = z_sb; p.z_sl = z_sl;
   p.b_sb = b_sb; p.b_sl = b_sl; p.c_sb = c_sb; p.c_sl = c_sl; p.y_sb = y_sb; p.y_sl = y_sl;
@@ -672,4 +649,41 @@ extern "C" int mb200_sscan_fwd(const void* x, const void* delta, const void* z, 
   if (z) vec = vec && z_sb % kv == 0 && z_sl % kv == 0;
   return dtype == MB200_F32 ? generic_launch_t<float>(p, N, vec, st)
                             : generic_launch_t<__nv_bfloat16>(p, N, vec, st);
+}
+
+// Forward carry pass of a split sequence: the state a span reaches from a zero state, and the span's decay
+// product, in one pass over x, delta, B (no y, no C, no saved states).
+extern "C" int mb200_sscan_fwd_carry(const void* x, const void* delta, const float* A, const void* Bm,
+                                     const float* delta_bias, float* h_out, float* p_out,
+                                     int64_t B, int64_t L, int64_t ED, int N,
+                                     int64_t x_sb, int64_t x_sl, int64_t d_sb, int64_t d_sl,
+                                     int64_t b_sb, int64_t b_sl, int dtype, int flags, void* stream) {
+  if (B < 0 || L < 0 || ED < 0) return MB200_EINVAL;
+  if (dtype != MB200_F32 && dtype != MB200_BF16) return MB200_EDTYPE;
+  if (N != 8 && N != 16 && N != 32 && N != 64) return MB200_ENSTATE;
+  if (B == 0 || ED == 0) return MB200_OK;
+  if (!h_out || !p_out || !A) return MB200_EINVAL;
+  if ((flags & MB200_DELTA_SOFTPLUS) && !delta_bias) return MB200_EINVAL;
+  if (flags & MB200_REVERSE) return MB200_EUNSUPPORTED;
+  if (!aligned16(h_out) || !aligned16(p_out)) return MB200_EALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (L > 0 && (!x || !delta || !Bm)) return MB200_EINVAL;
+  if (L > 0) {
+    SscanFwdParams p;
+    p.x = x; p.delta = delta; p.z = nullptr; p.A = A; p.Bm = Bm; p.Cm = Bm; p.D = nullptr;
+    p.delta_bias = delta_bias; p.h0 = nullptr; p.y = nullptr; p.hT = h_out; p.pT = p_out; p.carries = nullptr;
+    p.B = B; p.L = L; p.ED = ED;
+    p.x_sb = x_sb; p.x_sl = x_sl; p.d_sb = d_sb; p.d_sl = d_sl; p.z_sb = 0; p.z_sl = 0;
+    p.b_sb = b_sb; p.b_sl = b_sl; p.c_sb = b_sb; p.c_sl = b_sl; p.y_sb = 0; p.y_sl = 0;
+    p.flags = flags & (MB200_DELTA_SOFTPLUS | MB200_GENERAL_DECAY);
+    const int rc = mb200_fwd_tma_try(p, N, dtype, st);
+    if (rc <= 0) return rc;                        // launched (0) or failed hard (< 0)
+  }
+  // tensors the tensor-map path cannot take (or an empty span): the two pieces as separate launches
+  int rc = mb200_sscan_fwd(x, delta, nullptr, A, Bm, Bm, nullptr, delta_bias, nullptr, nullptr, h_out, nullptr, B, L, ED,
+                           N, x_sb, x_sl, d_sb, d_sl, 0, 0, b_sb, b_sl, b_sb, b_sl, 0, 0, dtype,
+                           flags & (MB200_DELTA_SOFTPLUS | MB200_GENERAL_DECAY), stream);
+  if (rc != MB200_OK) return rc;
+  return mb200_decay_prod(delta, A, delta_bias, p_out, B, L, ED, N, d_sb, d_sl, dtype, flags & MB200_DELTA_SOFTPLUS,
+                          stream);
 }

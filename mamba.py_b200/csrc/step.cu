@@ -148,6 +148,29 @@ __global__ void carry_fold_kernel(const float* __restrict__ P, const float* __re
   out[m] = cur;
 }
 
+// States entering pieces first .. first+num-1 of sequences cut into R pieces, in one launch.
+// P, S: (batch, R, M); init: (batch, M) or null; out: (batch, num, M).
+__global__ void carry_fold_range_kernel(const float* __restrict__ P, const float* __restrict__ S,
+                                        const float* __restrict__ init, float* __restrict__ out, int R,
+                                        int64_t M, int first, int num, int reverse) {
+  const int64_t m = int64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t bb = blockIdx.y;
+  if (m >= M) return;
+  P += bb * R * M; S += bb * R * M; out += bb * num * M;
+  float cur = init ? init[bb * M + m] : 0.f;
+  if (!reverse) {
+    for (int r = 0; r < first + num; ++r) {
+      if (r >= first) out[int64_t(r - first) * M + m] = cur;
+      if (r + 1 < first + num) cur = fmaf(P[int64_t(r) * M + m], cur, S[int64_t(r) * M + m]);
+    }
+  } else {
+    for (int r = R - 1; r >= first; --r) {
+      if (r < first + num) out[int64_t(r - first) * M + m] = cur;
+      if (r > first) cur = fmaf(P[int64_t(r) * M + m], cur, S[int64_t(r) * M + m]);
+    }
+  }
+}
+
 // P[b,e,n] = exp(A[e,n] * sum_t delta[b,t,e]); a CTA column-sums a strip of 32 channels.
 template <typename T>
 __global__ void decay_prod_kernel(const T* __restrict__ delta, const float* __restrict__ A,
@@ -280,6 +303,18 @@ extern "C" int mb200_carry_fold(const float* P, const float* S, float* out, int6
   if (!P || !S || !out) return MB200_EINVAL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   carry_fold_kernel<<<unsigned((M + 255) / 256), 256, 0, st>>>(P, S, out, R, M, rank, reverse);
+  return check_launch();
+}
+
+extern "C" int mb200_carry_fold_range(const float* P, const float* S, const float* init, float* out, int64_t batch,
+                                      int64_t R, int64_t M, int first, int num, int reverse, void* stream) {
+  if (batch < 0 || batch > 65535 || R < 1 || R > (1 << 20) || M < 0 || first < 0 || num < 1 || first + num > R)
+    return MB200_EINVAL;
+  if (M == 0 || batch == 0) return MB200_OK;
+  if (!P || !S || !out) return MB200_EINVAL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  dim3 grid(unsigned((M + 255) / 256), unsigned(batch));
+  carry_fold_range_kernel<<<grid, 256, 0, st>>>(P, S, init, out, int(R), M, first, num, reverse);
   return check_launch();
 }
 

@@ -22,125 +22,16 @@ import torch.nn.functional as F
 from . import _lib
 
 
-def _require_cuda(*ts):
-    for t in ts:
-        if t is not None and not t.is_cuda:
-            raise RuntimeError("mamba_b200 runs on CUDA tensors only (there is no CPU path)")
-
-
-def _rows(t: torch.Tensor | None, dtype) -> torch.Tensor | None:
-    """Cast to the activation dtype and make the last dim unit-stride (copy only if needed)."""
-    if t is None:
-        return None
-    if t.dtype != dtype:
-        t = t.to(dtype)
-    if t.stride(-1) != 1:
-        t = t.contiguous()
-    return t
-
-
-def _act_dtype(x: torch.Tensor, *others):
-    """Activation dtype the kernel runs in: bfloat16 only when EVERY activation tensor is bfloat16,
-    float32 as soon as one of them is (under autocast the reference keeps delta in float32 while x, B
-    and C are bfloat16, mambapy/mamba.py:264-265; rounding delta to bfloat16 would change the decay)."""
-    dts = {t.dtype for t in (x,) + others if t is not None}
-    for d in dts:
-        if d not in (torch.float32, torch.bfloat16):
-            raise TypeError(f"mamba_b200 kernels take float32 or bfloat16 activations, got {d}")
-    return torch.bfloat16 if dts == {torch.bfloat16} else torch.float32
-
-
-def _tensor_map_ok(t: torch.Tensor) -> bool:
-    """16-byte aligned base and byte strides: what a tiled tensor map of a (B, L, C) tensor needs."""
-    es = t.element_size()
-    return t.data_ptr() % 16 == 0 and (t.stride(0) * es) % 16 == 0 and (t.stride(1) * es) % 16 == 0
-
-
-def _f32(t):
-    return None if t is None else t.detach().float().contiguous()
-
-
-def sscan_fwd_raw(x, delta, A, Bm, Cm, D, z=None, delta_bias=None, h0=None,
-                  want_last=False, want_carries=False, want_y=True, reverse=False, general_decay=False):
-    """Launch the fused forward.  Tensors must already be prepared by the caller.
-
-    Returns (y, hT, carries); entries not asked for are None.  With `reverse` the scan runs from the
-    last timestep to the first; None is returned when the kernels cannot do that for these tensors
-    (the caller then flips them itself).  `general_decay` switches off the kernels' own shortcut for an
-    A with the S4D-real structure (every decay then gets its own exponential)."""
-    lib = _lib.load()
-    Bsz, L, ED = x.shape
-    N = A.shape[1]
-    dev = x.device
-    y = torch.empty((Bsz, L, ED), dtype=x.dtype, device=dev) if want_y else None
-    hT = torch.empty((Bsz, ED, N), dtype=torch.float32, device=dev) if want_last else None
-    chunk = lib.mb200_sscan_chunk()
-    carries = (torch.empty((Bsz, (L + chunk - 1) // chunk, ED, N), dtype=torch.float32, device=dev)
-               if want_carries else None)
-    flags = ((_lib.DELTA_SOFTPLUS if delta_bias is not None else 0) | (_lib.REVERSE if reverse else 0)
-             | (_lib.GENERAL_DECAY if general_decay else 0))
-    zs = (z.stride(0), z.stride(1)) if z is not None else (0, 0)
-    ys = (y.stride(0), y.stride(1)) if y is not None else (0, 0)
-    with torch.cuda.device(dev):
-        rc = lib.mb200_sscan_fwd(
-            x.data_ptr(), delta.data_ptr(), _lib.ptr(z), A.data_ptr(), Bm.data_ptr(), Cm.data_ptr(),
-            _lib.ptr(D), _lib.ptr(delta_bias), _lib.ptr(h0), _lib.ptr(y), _lib.ptr(hT),
-            _lib.ptr(carries), Bsz, L, ED, N,
-            x.stride(0), x.stride(1), delta.stride(0), delta.stride(1), zs[0], zs[1],
-            Bm.stride(0), Bm.stride(1), Cm.stride(0), Cm.stride(1), ys[0], ys[1],
-            _lib.dtype_code(x.dtype), flags, _lib.current_stream(dev))
-    if reverse and rc == _lib.EUNSUPPORTED:
-        return None
-    _lib.check(rc, "mb200_sscan_fwd")
-    _lib.check_status(dev, "mb200_sscan_fwd")
-    return y, hT, carries
-
-
-def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None, want_g_out=False,
-                  reverse=False, general_decay=False):
-    """Launch the fused backward.  Returns (dx, ddelta, dz, dB, dC, dA, dD, dbias, g_out).
-
-    `reverse` must be what the forward that produced `carries` ran with."""
-    lib = _lib.load()
-    Bsz, L, ED = x.shape
-    N = A.shape[1]
-    dev = x.device
-    dx = torch.empty((Bsz, L, ED), dtype=x.dtype, device=dev)
-    dd = torch.empty_like(dx)
-    dz = torch.empty_like(dx) if z is not None else None
-    # every buffer the kernel accumulates into comes out of ONE zero-filled allocation (one fill launch)
-    nBC, nA = Bsz * L * N, ED * N
-    acc = torch.zeros(2 * nBC + nA + 2 * ED, dtype=torch.float32, device=dev)
-    dB = acc[:nBC].view(Bsz, L, N)
-    dC = acc[nBC:2 * nBC].view(Bsz, L, N)
-    dA = acc[2 * nBC:2 * nBC + nA].view(ED, N)
-    dD = acc[2 * nBC + nA:2 * nBC + nA + ED]
-    dbias = acc[2 * nBC + nA + ED:] if delta_bias is not None else None
-    g_out = torch.empty((Bsz, ED, N), dtype=torch.float32, device=dev) if want_g_out else None
-    flags = ((_lib.DELTA_SOFTPLUS if delta_bias is not None else 0) | (_lib.REVERSE if reverse else 0)
-             | (_lib.GENERAL_DECAY if general_decay else 0))
-    zs = (z.stride(0), z.stride(1)) if z is not None else (0, 0)
-    dzs = (dz.stride(0), dz.stride(1)) if dz is not None else (0, 0)
-    with torch.cuda.device(dev):
-        rc = lib.mb200_sscan_bwd(
-            x.data_ptr(), delta.data_ptr(), _lib.ptr(z), A.data_ptr(), Bm.data_ptr(), Cm.data_ptr(),
-            _lib.ptr(D), _lib.ptr(delta_bias), dy.data_ptr(), carries.data_ptr(), _lib.ptr(g_in),
-            dx.data_ptr(), dd.data_ptr(), _lib.ptr(dz), dB.data_ptr(), dC.data_ptr(), dA.data_ptr(),
-            dD.data_ptr(), _lib.ptr(dbias), _lib.ptr(g_out), Bsz, L, ED, N,
-            x.stride(0), x.stride(1), delta.stride(0), delta.stride(1), zs[0], zs[1],
-            Bm.stride(0), Bm.stride(1), Cm.stride(0), Cm.stride(1), dy.stride(0), dy.stride(1),
-            dx.stride(0), dx.stride(1), dd.stride(0), dd.stride(1), dzs[0], dzs[1],
-            _lib.dtype_code(x.dtype), flags, _lib.current_stream(dev))
-    _lib.check(rc, "mb200_sscan_bwd")
-    _lib.check_status(dev, "mb200_sscan_bwd")
-    return dx, dd, dz, dB, dC, dA, dD, dbias, g_out
+from .kernels import (_require_cuda, _rows, _act_dtype, _tensor_map_ok, _f32, sscan_fwd_raw, sscan_bwd_raw,
+                      sscan_fwd_carry_raw, sscan_bwd_carry_raw, carry_fold_range)
+from .split import CudaOps, pick_subshards, split_forward, split_backward
 
 
 class SelectiveScanFn(torch.autograd.Function):
     """y (and optionally the last state) of the fused scan; gradients for every input."""
 
     @staticmethod
-    def forward(ctx, x, delta, A, Bm, Cm, D, z, delta_bias, h0, return_last_state, reverse=False):
+    def forward(ctx, x, delta, A, Bm, Cm, D, z, delta_bias, h0, return_last_state, reverse=False, subshards=None):
         _require_cuda(x, delta, A, Bm, Cm, D, z, delta_bias, h0)
         dt = _act_dtype(x, delta, z, Bm, Cm)
         xs, ds, zs = _rows(x, dt), _rows(delta, dt), _rows(z, dt)
@@ -150,7 +41,17 @@ class SelectiveScanFn(torch.autograd.Function):
                          for t in (x, delta, A, Bm, Cm, D, z, delta_bias, h0))
         out = None
         ctx.flipped = False
-        if reverse and not (needs_grad and A32.shape[1] != 16):    # the reverse backward exists for d_state 16
+        P_all = None
+        # Few batch rows: cut every row into S consecutive pieces that run side by side (split.py); the
+        # reference's own published shapes are all batch 1, i.e. 64 work items for a 148-SM GPU.
+        S = subshards if subshards else pick_subshards(xs.shape[0], xs.shape[1], xs.shape[2], 1)
+        if reverse or S < 1 or xs.shape[1] % (16 * S) or xs.shape[1] == 0:
+            S = 1
+        if S > 1:
+            y, _, P_all, carries, hT = split_forward(CudaOps, None, xs, ds, A32, Bs, Cs, D32, zs, b32, h0=h032,
+                                                     want_carries=needs_grad, subshards=S)
+            out = (y, hT if return_last_state else None, carries)
+        if out is None and reverse and not (needs_grad and A32.shape[1] != 16):    # the reverse backward exists for d_state 16
             out = sscan_fwd_raw(xs, ds, A32, Bs, Cs, D32, zs, b32, h032, want_last=return_last_state,
                                 want_carries=needs_grad, reverse=True)
         if reverse and out is None:
@@ -164,7 +65,8 @@ class SelectiveScanFn(torch.autograd.Function):
         if ctx.flipped:
             y = y.flip(1)
         ctx.reverse = reverse and not ctx.flipped
-        ctx.save_for_backward(xs, ds, A32, Bs, Cs, D32, zs, b32, carries)
+        ctx.subshards = S
+        ctx.save_for_backward(xs, ds, A32, Bs, Cs, D32, zs, b32, carries, P_all)
         ctx.in_dtypes = tuple(None if t is None else t.dtype
                               for t in (x, delta, A, Bm, Cm, D, z, delta_bias, h0))
         ctx.has_h0 = h0 is not None
@@ -175,8 +77,15 @@ class SelectiveScanFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy, *unused):
-        xs, ds, A32, Bs, Cs, D32, zs, b32, carries = ctx.saved_tensors
+        xs, ds, A32, Bs, Cs, D32, zs, b32, carries, P_all = ctx.saved_tensors
         dy = _rows(dy.flip(1) if ctx.flipped else dy, xs.dtype)
+        if ctx.subshards > 1:
+            dx, dd, dz, dB, dC, dA, dD, dbias, g_out = split_backward(
+                CudaOps, None, xs, ds, A32, Bs, Cs, D32, zs, b32, dy, carries, P_all, subshards=ctx.subshards)
+            tx, td, tA, tB, tC, tD, tz, tb, th = ctx.in_dtypes
+            cast = lambda g, t: None if (g is None or t is None) else g.to(t)
+            return (cast(dx, tx), cast(dd, td), cast(dA, tA), cast(dB, tB), cast(dC, tC), cast(dD, tD),
+                    cast(dz, tz), cast(dbias, tb), cast(g_out if ctx.has_h0 else None, th), None, None, None)
         if ctx.reverse and not _tensor_map_ok(dy):
             # the in-kernel reverse backward exists on the tensor-map path only; an upstream gradient
             # that is an offset or narrow view of something wider is copied to a dense tensor first
@@ -188,11 +97,11 @@ class SelectiveScanFn(torch.autograd.Function):
         tx, td, tA, tB, tC, tD, tz, tb, th = ctx.in_dtypes
         cast = lambda g, t: None if (g is None or t is None) else g.to(t)
         return (cast(dx, tx), cast(dd, td), cast(dA, tA), cast(dB, tB), cast(dC, tC),
-                cast(dD, tD), cast(dz, tz), cast(dbias, tb), cast(g_out, th), None, None)
+                cast(dD, tD), cast(dz, tz), cast(dbias, tb), cast(g_out, th), None, None, None)
 
 
 def selective_scan_fn(x, delta, A, B, C, D=None, z=None, delta_bias=None, h0=None,
-                      return_last_state=False, reverse=False):
+                      return_last_state=False, reverse=False, subshards=None):
     """Fused selective scan.
 
     x, delta, z : (B, L, ED)   B, C : (B, L, N)   A : (ED, N)   D : (ED)
@@ -206,8 +115,12 @@ def selective_scan_fn(x, delta, A, B, C, D=None, z=None, delta_bias=None, h0=Non
     sequence, scans and flips back (mambapy/vim.py:228-261).  The kernels do it in place when the
     tensors meet the tensor-map alignment rules (and d_state is 16 if gradients are needed);
     otherwise this function flips, as the reference does.
+
+    With few batch rows the sequence is cut into `subshards` consecutive pieces that are scanned side by
+    side (two extra carry passes, see split.py): None picks the number from the shape, 1 never cuts, any
+    other value is used if L is a multiple of 16 * subshards.
     """
-    return SelectiveScanFn.apply(x, delta, A, B, C, D, z, delta_bias, h0, return_last_state, reverse)
+    return SelectiveScanFn.apply(x, delta, A, B, C, D, z, delta_bias, h0, return_last_state, reverse, subshards)
 
 
 # ----------------------------------------------------------------- MambaBlock method drop-ins

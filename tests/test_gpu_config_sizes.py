@@ -25,17 +25,19 @@ def _grad_check(got, want, rtol, atol, ctx):
         assert_close(got[k], w.float(), rtol, atol * scale * 4, f"grad {k} {ctx}")
 
 
-@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
-def test_layer_130m_scan_as_benchmarked(dtype):
+@pytest.mark.parametrize("dtype,subshards", [(torch.bfloat16, 1), (torch.float32, 1), (torch.bfloat16, None)])
+def test_layer_130m_scan_as_benchmarked(dtype, subshards):
     """The instantiation bench.py times: L = 2048, ED = 1536, N = 16, softplus(delta + bias) inside,
-    gated, the reference's dt-bias and S4D-real initialisation; bf16 I/O (and once in float32)."""
+    gated, the reference's dt-bias and S4D-real initialisation; bf16 I/O (and once in float32).  With
+    subshards = 1 the row goes through one launch per direction, as the rows of the benchmark's batch of 8
+    do; with None the library cuts the lone row into pieces, as it does for any batch-1 call."""
     import bench_workloads
     import mamba_b200
     w = bench_workloads.layer_130m_scan_inputs(1002, torch.device(DEV), Bsz=1, L=2048, dtype=dtype)
     names = ("x", "delta_raw", "z", "B", "C", "A", "D", "delta_bias")
     lv = {k: w[k].clone().requires_grad_() for k in names}
     y = mamba_b200.selective_scan_fn(lv["x"], lv["delta_raw"], lv["A"], lv["B"], lv["C"], lv["D"], z=lv["z"],
-                                     delta_bias=lv["delta_bias"])
+                                     delta_bias=lv["delta_bias"], subshards=subshards)
     y.backward(w["dy"])
     assert y.dtype == dtype
     inp = dict(x=w["x"], delta=w["delta_raw"], z=w["z"], B=w["B"], C=w["C"], A=w["A"], D=w["D"], gy=w["dy"])
@@ -135,7 +137,7 @@ def test_bf16_long_enough_to_wrap_the_ring_twice(Bsz, L, ED, reverse):
         yk, hk, gk = _kernel_reversed(inp, torch.bfloat16, True, None, bias)
     else:
         yo, ho, go = _oracle(inp, gated=True, bias=bias)
-        yk, hk, gk = _kernel(inp, torch.bfloat16, gated=True, bias=bias)
+        yk, hk, gk = _kernel(inp, torch.bfloat16, gated=True, bias=bias, subshards=1)     # one launch over all of L
     assert_close(yk, yo.float(), BF_RTOL, BF_ATOL * max(1.0, yo.abs().max().item()), "y")
     assert_close(hk, ho.float(), RTOL, ATOL * max(1.0, ho.abs().max().item()), "state")
     _grad_check(gk, go, BF_RTOL, BF_ATOL, f"L={L}")

@@ -24,19 +24,21 @@ def _emulate(inp, R, dtype, bias=None):
     L = x.shape[1]
     Ls = L // R
     sl = lambda t, r: t[:, r * Ls:(r + 1) * Ls] if r < R - 1 else t[:, r * Ls:]
-    S = torch.stack([K.carry_pass(sl(x, r), sl(dl, r), A, sl(Bm, r), sl(Cm, r), b) for r in range(R)])
-    P = torch.stack([K.decay_prod(sl(dl, r), A, b) for r in range(R)])
+    SP = [K.carry_pass(sl(x, r), sl(dl, r), A, sl(Bm, r), sl(Cm, r), b) for r in range(R)]
+    S = torch.stack([sp[0] for sp in SP], dim=1)                    # (B, R, ED, N): state reached from zero
+    P = torch.stack([sp[1] for sp in SP], dim=1)                    # decay product of every shard
+    h_in = K.fold_range(P, S, None, 0, R, False)                    # state entering every shard, one launch
     ys, cars = [], []
     for r in range(R):
-        h_in = K.fold(P, S, r, False)
-        y, hT, car = K.full_fwd(sl(x, r), sl(dl, r), A, sl(Bm, r), sl(Cm, r), D, sl(z, r), b, h_in, True)
+        y, hT, car = K.full_fwd(sl(x, r), sl(dl, r), A, sl(Bm, r), sl(Cm, r), D, sl(z, r), b, h_in[:, r].contiguous(), True)
         ys.append(y)
         cars.append(car)
-    G = torch.stack([K.rev_carry_pass(sl(dl, r), sl(z, r), sl(dy, r), sl(Cm, r), A, b) for r in range(R)])
+    G = torch.stack([K.rev_carry_pass(sl(dl, r), sl(z, r), sl(dy, r), sl(Cm, r), A, b) for r in range(R)], dim=1)
+    g_in = K.fold_range(P, G, None, 0, R, True)
     outs = []
     for r in range(R):
-        g_in = K.fold(P, G, r, True)
-        outs.append(K.full_bwd(sl(x, r), sl(dl, r), A, sl(Bm, r), sl(Cm, r), D, sl(z, r), b, sl(dy, r), cars[r], g_in))
+        outs.append(K.full_bwd(sl(x, r), sl(dl, r), A, sl(Bm, r), sl(Cm, r), D, sl(z, r), b, sl(dy, r), cars[r],
+                               g_in[:, r].contiguous()))
     cat = lambda i: torch.cat([o[i] for o in outs], 1)
     tot = lambda i: sum(o[i] for o in outs)
     return dict(y=torch.cat(ys, 1), x=cat(0), delta=cat(1), z=cat(2), B=cat(3), C=cat(4), A=tot(5), D=tot(6),

@@ -33,7 +33,7 @@ def _oracle(inp, gated=True, h0=None, bias=None):
     return y.detach(), hT.detach(), grads
 
 
-def _kernel(inp, dtype, gated=True, h0=None, bias=None):
+def _kernel(inp, dtype, gated=True, h0=None, bias=None, subshards=None):
     import mamba_b200
     act = lambda k: inp[k].to(DEV).to(dtype).requires_grad_()
     par = lambda k: inp[k].to(DEV).requires_grad_()
@@ -42,7 +42,7 @@ def _kernel(inp, dtype, gated=True, h0=None, bias=None):
     h0l = None if h0 is None else h0.to(DEV).requires_grad_()
     y, hT = mamba_b200.selective_scan_fn(leaves["x"], leaves["delta"], leaves["A"], leaves["B"], leaves["C"],
                                          leaves["D"], z=leaves["z"] if gated else None, delta_bias=bl,
-                                         h0=h0l, return_last_state=True)
+                                         h0=h0l, return_last_state=True, subshards=subshards)
     y.backward(inp["gy"].to(DEV).to(dtype))
     grads = {k: (v.grad if v.grad is not None else torch.zeros_like(v)) for k, v in leaves.items()}
     if bl is not None:
@@ -52,9 +52,9 @@ def _kernel(inp, dtype, gated=True, h0=None, bias=None):
     return y.detach(), hT.detach(), grads
 
 
-def _compare(inp, dtype, rtol, atol, **kw):
+def _compare(inp, dtype, rtol, atol, subshards=None, **kw):
     yo, ho, go = _oracle(inp, **kw)
-    yk, hk, gk = _kernel(inp, dtype, **kw)
+    yk, hk, gk = _kernel(inp, dtype, subshards=subshards, **kw)
     assert yk.dtype == dtype
     assert_close(yk, yo.float(), rtol, atol, "y")
     assert_close(hk, ho.float(), rtol, atol, "last state")
@@ -214,3 +214,33 @@ def test_empty_and_errors():
     with pytest.raises(RuntimeError):            # CPU tensors: no fallback
         mamba_b200.selective_scan_fn(torch.zeros(1, 4, 8), torch.zeros(1, 4, 8), -torch.ones(8, 16),
                                      torch.zeros(1, 4, 16), torch.zeros(1, 4, 16), torch.zeros(8))
+
+
+@pytest.mark.parametrize("Bsz,L,ED,S,use_h0,use_bias", [(1, 1024, 64, None, False, False), (2, 512, 40, 4, True, True),
+                                                       (1, 2048, 96, 16, True, False), (3, 256, 32, 2, False, True)])
+def test_rows_cut_into_pieces_match_the_oracle(Bsz, L, ED, S, use_h0, use_bias):
+    """Few batch rows: every row is cut into S pieces scanned side by side (carry pass, fold, full pass, and
+    the mirror image in the backward).  Same answer as the scan of the whole row, including the incoming
+    state, its gradient and the outgoing state; S = None lets the library choose (and it must choose > 1)."""
+    from mamba_b200.split import pick_subshards
+    inp = scan_inputs(600 + L + ED, Bsz, L, ED, 16, structured_A=False, big_delta=True)
+    g = torch.Generator().manual_seed(L)
+    h0 = torch.randn(Bsz, ED, 16, generator=g) if use_h0 else None
+    bias = None
+    if use_bias:
+        bias = torch.randn(ED, generator=g) * 0.5 - 3.0
+        inp["delta"] = torch.randn(Bsz, L, ED, generator=g)
+    if S is None:
+        assert pick_subshards(Bsz, L, ED, 1) > 1
+    _compare(inp, torch.float32, RTOL, ATOL, subshards=S, gated=True, h0=h0, bias=bias)
+
+
+def test_rows_cut_into_pieces_bf16_long():
+    inp = scan_inputs(77, 1, 4096, 128, 16, dtype=torch.bfloat16)
+    yo, ho, go = _oracle(inp)
+    yk, hk, gk = _kernel(inp, torch.bfloat16, subshards=8)
+    assert_close(yk, yo.float(), BF_RTOL, BF_ATOL, "y")
+    assert_close(hk, ho.float(), 1e-3, 1e-4, "last state")
+    for k in ("x", "delta", "z", "B", "C", "A", "D"):
+        scale = max(1.0, go[k].abs().max().item())
+        assert_close(gk[k], go[k].float(), BF_RTOL, BF_ATOL * scale, f"grad {k}")

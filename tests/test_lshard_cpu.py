@@ -21,22 +21,21 @@ class OracleOps:
 
     @staticmethod
     def carry_pass(x, delta, A, Bm, Cm, bias):
-        _, h = O.selective_scan_f64(x, OracleOps._delta(delta, bias), A, Bm, Cm, torch.zeros(x.shape[2]),
-                                    return_last_state=True)
-        return h
+        d = OracleOps._delta(delta, bias)
+        _, h = O.selective_scan_f64(x, d, A, Bm, Cm, torch.zeros(x.shape[2]), return_last_state=True)
+        return h, torch.exp(d.double().sum(1).unsqueeze(-1) * A.double())
 
     @staticmethod
-    def decay_prod(delta, A, bias):
-        s = OracleOps._delta(delta, bias).double().sum(1)                  # (B, ED)
-        return torch.exp(s.unsqueeze(-1) * A.double())
-
-    @staticmethod
-    def fold(P_all, S_all, rank, reverse):
-        cur = torch.zeros_like(P_all[0])
-        order = range(P_all.shape[0] - 1, rank, -1) if reverse else range(rank)
-        for r in order:
-            cur = P_all[r] * cur + S_all[r]
-        return cur
+    def fold_range(P_all, S_all, init, first, num, reverse):
+        """P_all, S_all: (B, pieces, ED, N) -> (B, num, ED, N): state entering pieces first .. first+num-1."""
+        R = P_all.shape[1]
+        out = []
+        for i in range(first, first + num):
+            cur = torch.zeros_like(P_all[:, 0]) if init is None else init.clone()
+            for r in (range(R - 1, i, -1) if reverse else range(i)):
+                cur = P_all[:, r] * cur + S_all[:, r]
+            out.append(cur)
+        return torch.stack(out, dim=1)
 
     @staticmethod
     def full_fwd(x, delta, A, Bm, Cm, D, z, bias, h_in, want_carries):
@@ -130,6 +129,7 @@ def test_two_cpu_ranks_reproduce_the_single_sequence(use_bias, S):
 def test_pick_subshards():
     from mamba_b200.lshard import pick_subshards
     assert pick_subshards(8, 2048, 1536, 1) == 1            # already enough rows x channel tiles
-    assert pick_subshards(1, 131072, 5120, 1) == 8          # one long row: cut it up
-    assert pick_subshards(1, 16384, 5120, 8) == 8
+    assert pick_subshards(1, 65536, 2048, 1) == 8           # one long row of a 1024-wide model: cut it up
+    assert pick_subshards(1, 16384, 5120, 8) > 1            # several ranks: the carry passes exist anyway
     assert pick_subshards(1, 40, 5120, 1) == 1              # not divisible into 16-step pieces
+    assert pick_subshards(1, 256, 2048, 1) <= 2             # pieces stay at least 128 timesteps long
