@@ -289,6 +289,26 @@ int mb200_rmsnorm_bwd(const void* x, const float* weight, const float* rstd, con
                       float* dweight, int64_t rows, int64_t D, int64_t x_rs, int64_t dy_rs, int64_t dx_rs,
                       int dtype, void* stream);
 
+/* ---- Residual add fused with the RMSNorm that follows it.  A stack of blocks computes
+ * x_{l+1} = mixer(norm(x_l)) + x_l (ResidualBlock.forward, mambapy/mamba.py:106-112, looped by
+ * Mamba.forward, mambapy/mamba.py:77-85); the add of layer l and the norm of layer l+1 become one pass:
+ *   s = x + res_in (res_in NULL: s = x);   res_out = s;   y = s * rsqrt(mean(s^2) + eps) * weight.
+ * x: the previous mixer's output; res_in / res_out: the residual stream; y: the next mixer's input.  Each of
+ * the three has its own element type (under autocast the mixer works in bfloat16 while the residual stream
+ * stays float32); served triples (x, res, y): fff, ffb, bff, bfb, bbb (MB200_EUNSUPPORTED otherwise).
+ * Row strides in elements; rstd (rows) float32, optional, is what mb200_add_rmsnorm_bwd needs. */
+int mb200_add_rmsnorm_fwd(const void* x, const void* res_in, const float* weight, void* res_out, void* y,
+                          float* rstd, int64_t rows, int64_t D, int64_t x_rs, int64_t ri_rs, int64_t ro_rs,
+                          int64_t y_rs, float eps, int dtype_x, int dtype_res, int dtype_y, void* stream);
+
+/* Backward of mb200_add_rmsnorm_fwd: ds = d(loss)/d s = RMSNorm backward of dy at s, plus dres (the gradient
+ * that reaches res_out from later layers; NULL = none).  ds has the residual stream's type and is the gradient
+ * of BOTH x and res_in.  dweight (D) float32 or NULL, accumulated into; D <= 12288 when it is given. */
+int mb200_add_rmsnorm_bwd(const void* s, const float* weight, const float* rstd, const void* dy,
+                          const void* dres, void* ds, float* dweight, int64_t rows, int64_t D,
+                          int64_t s_rs, int64_t dy_rs, int64_t dr_rs, int64_t ds_rs, int dtype_res,
+                          int dtype_y, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -12,10 +12,10 @@ The package is importable as `mamba_b200`; its directory carries the project nam
 """
 from .pscan import PScan, pscan, npo2, pad_npo2
 from .mamba import (selective_scan_fn, selective_scan, selective_scan_seq, ssm_step, step,
-                    ssm_step_fn, conv_step_fn, causal_conv1d_silu, rms_norm)
+                    ssm_step_fn, conv_step_fn, causal_conv1d_silu, rms_norm, add_rms_norm)
 from .patch import install, uninstall, installed
 from ._lib import device_status
 
 __all__ = ["PScan", "pscan", "npo2", "pad_npo2", "selective_scan_fn", "selective_scan",
-           "selective_scan_seq", "ssm_step", "step", "ssm_step_fn", "conv_step_fn", "causal_conv1d_silu", "rms_norm",
+           "selective_scan_seq", "ssm_step", "step", "ssm_step_fn", "conv_step_fn", "causal_conv1d_silu", "rms_norm", "add_rms_norm",
            "install", "uninstall", "installed", "device_status"]

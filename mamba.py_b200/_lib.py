@@ -39,6 +39,8 @@ _SIGNATURES = {
     "mb200_conv1d_silu_bwd": (_int, [_ptr] * 7 + [_i64] * 3 + [_int] + [_i64] * 6 + [_int, _ptr]),
     "mb200_rmsnorm_fwd": (_int, [_ptr] * 4 + [_i64] * 4 + [C.c_float, _int, _ptr]),
     "mb200_rmsnorm_bwd": (_int, [_ptr] * 6 + [_i64] * 5 + [_int, _ptr]),
+    "mb200_add_rmsnorm_fwd": (_int, [_ptr] * 6 + [_i64] * 6 + [C.c_float, _int, _int, _int, _ptr]),
+    "mb200_add_rmsnorm_bwd": (_int, [_ptr] * 7 + [_i64] * 6 + [_int, _int, _ptr]),
     "mb200_carry_fold": (_int, [_ptr] * 3 + [_i64] * 2 + [_int, _int, _ptr]),
     "mb200_carry_fold_range": (_int, [_ptr] * 4 + [_i64] * 3 + [_int, _int, _int, _ptr]),
     "mb200_sscan_fwd_carry": (_int, [_ptr] * 7 + [_i64] * 3 + [_int] + [_i64] * 6 + [_int, _int, _ptr]),

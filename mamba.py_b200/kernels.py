@@ -87,7 +87,7 @@ def sscan_fwd_raw(x, delta, A, Bm, Cm, D, z=None, delta_bias=None, h0=None,
 
 
 def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None, want_g_out=False,
-                  reverse=False, general_decay=False):
+                  reverse=False, general_decay=False, out_dz=None):
     """Launch the fused backward.  Returns (dx, ddelta, dz, dB, dC, dA, dD, dbias, g_out).
 
     `reverse` must be what the forward that produced `carries` ran with."""
@@ -97,7 +97,8 @@ def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None,
     dev = x.device
     dx = torch.empty((Bsz, L, ED), dtype=x.dtype, device=dev)
     dd = torch.empty_like(dx)
-    dz = torch.empty_like(dx) if z is not None else None
+    # dz may be written straight into a caller's (strided) view, e.g. the second half of d(xz)
+    dz = (out_dz if out_dz is not None else torch.empty_like(dx)) if z is not None else None
     # every buffer the kernel accumulates into comes out of ONE zero-filled allocation (one fill launch)
     nBC, nA = Bsz * L * N, ED * N
     acc = torch.zeros(2 * nBC + nA + 2 * ED, dtype=torch.float32, device=dev)
@@ -128,8 +129,8 @@ def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None,
 
 
 def sscan_fwd_carry_raw(x, delta, A, Bm, delta_bias=None):
-    """Forward carry pass of a span: (state reached from a zero state, decay product of the span), both
-    (B, ED, N) float32, from one pass over x, delta, B."""
+    """Forward carry pass of a span, one pass over x, delta, B.  Returns one (2, B, ED, N) float32 tensor:
+    [0] the span's decay product exp(A * sum_t delta), [1] the state reached from a zero state."""
     lib = _lib.load()
     Bsz, L, ED = x.shape
     N = A.shape[1]
@@ -138,12 +139,12 @@ def sscan_fwd_carry_raw(x, delta, A, Bm, delta_bias=None):
     flags = _lib.DELTA_SOFTPLUS if delta_bias is not None else 0
     with torch.cuda.device(dev):
         rc = lib.mb200_sscan_fwd_carry(x.data_ptr(), delta.data_ptr(), A.data_ptr(), Bm.data_ptr(), _lib.ptr(delta_bias),
-                                       out[0].data_ptr(), out[1].data_ptr(), Bsz, L, ED, N, x.stride(0), x.stride(1),
+                                       out[1].data_ptr(), out[0].data_ptr(), Bsz, L, ED, N, x.stride(0), x.stride(1),
                                        delta.stride(0), delta.stride(1), Bm.stride(0), Bm.stride(1),
                                        _lib.dtype_code(x.dtype), flags, _lib.current_stream(dev))
     _lib.check(rc, "mb200_sscan_fwd_carry")
     _lib.check_status(dev, "mb200_sscan_fwd_carry")
-    return out[0], out[1]
+    return out
 
 
 def sscan_bwd_carry_raw(delta, z, dy, Cm, A, delta_bias=None):
@@ -179,3 +180,33 @@ def carry_fold_range(P_all, S_all, init, first, num, reverse):
                                         first, num, int(reverse), _lib.current_stream(P_all.device))
     _lib.check(rc, "mb200_carry_fold_range")
     return out
+
+
+def conv1d_silu_fwd_raw(xs, w32, b32):
+    """silu(depthwise causal conv1d(x)), d_conv 4, on (B, L, ED) with any batch / row strides."""
+    lib = _lib.load()
+    Bsz, L, ED = xs.shape
+    y = torch.empty((Bsz, L, ED), dtype=xs.dtype, device=xs.device)
+    with torch.cuda.device(xs.device):
+        rc = lib.mb200_conv1d_silu_fwd(xs.data_ptr(), w32.data_ptr(), _lib.ptr(b32), y.data_ptr(), Bsz, L, ED,
+                                       w32.shape[1], xs.stride(0), xs.stride(1), y.stride(0), y.stride(1),
+                                       _lib.dtype_code(xs.dtype), _lib.current_stream(xs.device))
+    _lib.check(rc, "mb200_conv1d_silu_fwd")
+    return y
+
+
+def conv1d_silu_bwd_raw(xs, w32, b32, dy, out_dx=None):
+    """Backward of conv1d_silu_fwd_raw.  Returns (dx, dw (ED, K) float32, db (ED) float32 or None); dx may be a
+    caller's (strided) view."""
+    lib = _lib.load()
+    Bsz, L, ED = xs.shape
+    dx = out_dx if out_dx is not None else torch.empty_like(xs)
+    dw = torch.zeros_like(w32)
+    db = torch.zeros(ED, dtype=torch.float32, device=xs.device) if b32 is not None else None
+    with torch.cuda.device(xs.device):
+        rc = lib.mb200_conv1d_silu_bwd(xs.data_ptr(), w32.data_ptr(), _lib.ptr(b32), dy.data_ptr(), dx.data_ptr(),
+                                       dw.data_ptr(), _lib.ptr(db), Bsz, L, ED, w32.shape[1], xs.stride(0), xs.stride(1),
+                                       dy.stride(0), dy.stride(1), dx.stride(0), dx.stride(1),
+                                       _lib.dtype_code(xs.dtype), _lib.current_stream(xs.device))
+    _lib.check(rc, "mb200_conv1d_silu_bwd")
+    return dx, dw, db

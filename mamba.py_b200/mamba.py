@@ -23,7 +23,8 @@ from . import _lib
 
 
 from .kernels import (_require_cuda, _rows, _act_dtype, _tensor_map_ok, _f32, sscan_fwd_raw, sscan_bwd_raw,
-                      sscan_fwd_carry_raw, sscan_bwd_carry_raw, carry_fold_range)
+                      sscan_fwd_carry_raw, sscan_bwd_carry_raw, carry_fold_range, conv1d_silu_fwd_raw,
+                      conv1d_silu_bwd_raw)
 from .split import CudaOps, pick_subshards, split_forward, split_backward
 
 
@@ -298,6 +299,99 @@ def rms_norm(x, weight=None, eps=1e-5):
     return RMSNormFn.apply(x, weight, eps)
 
 
+class AddRMSNormFn(torch.autograd.Function):
+    """(y, s) with s = x + residual and y = RMSNorm(s), one pass (mb200_add_rmsnorm_fwd)."""
+
+    @staticmethod
+    def forward(ctx, x, residual, weight, eps, y_dtype):
+        lib = _lib.load()
+        D = x.shape[-1]
+        x2 = x.reshape(-1, D)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        r2 = None
+        res_dtype = x.dtype
+        if residual is not None:
+            r2 = residual.reshape(-1, D)
+            if r2.stride(-1) != 1:
+                r2 = r2.contiguous()
+            res_dtype = torch.promote_types(x.dtype, residual.dtype)       # what `x + residual` would give
+            if r2.dtype != res_dtype:
+                r2 = r2.to(res_dtype)
+        rows = x2.shape[0]
+        w32 = None if weight is None else _f32(weight)
+        s = torch.empty((rows, D), dtype=res_dtype, device=x.device)
+        y = torch.empty((rows, D), dtype=y_dtype, device=x.device)
+        rstd = torch.empty((rows,), dtype=torch.float32, device=x.device)
+        with torch.cuda.device(x.device):
+            rc = lib.mb200_add_rmsnorm_fwd(x2.data_ptr(), _lib.ptr(r2), _lib.ptr(w32), s.data_ptr(), y.data_ptr(),
+                                           rstd.data_ptr(), rows, D, x2.stride(0), 0 if r2 is None else r2.stride(0),
+                                           s.stride(0), y.stride(0), float(eps), _lib.dtype_code(x2.dtype),
+                                           _lib.dtype_code(res_dtype), _lib.dtype_code(y_dtype),
+                                           _lib.current_stream(x.device))
+        _lib.check(rc, "mb200_add_rmsnorm_fwd")
+        ctx.save_for_backward(s, w32, rstd)
+        ctx.meta = (x.shape, x.dtype, None if residual is None else residual.dtype,
+                    None if weight is None else weight.dtype)
+        return y.view(x.shape), s.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy, ds_out):
+        s, w32, rstd = ctx.saved_tensors
+        shape, tx, tr, tw = ctx.meta
+        lib = _lib.load()
+        rows, D = s.shape
+        y_dtype = dy.dtype if dy.dtype in (torch.float32, torch.bfloat16) else torch.float32
+        dy2 = dy.reshape(rows, D)
+        if dy2.dtype != y_dtype or dy2.stride(-1) != 1:
+            dy2 = dy2.to(y_dtype).contiguous()
+        if s.dtype == torch.bfloat16 and y_dtype != torch.bfloat16:
+            dy2, y_dtype = dy2.to(torch.bfloat16), torch.bfloat16
+        dr2 = None
+        if ds_out is not None:
+            dr2 = ds_out.reshape(rows, D)
+            if dr2.dtype != s.dtype or dr2.stride(-1) != 1:
+                dr2 = dr2.to(s.dtype).contiguous()
+        ds = torch.empty_like(s)
+        dw = torch.zeros(D, dtype=torch.float32, device=s.device) if w32 is not None else None
+        with torch.cuda.device(s.device):
+            rc = lib.mb200_add_rmsnorm_bwd(s.data_ptr(), _lib.ptr(w32), rstd.data_ptr(), dy2.data_ptr(), _lib.ptr(dr2),
+                                           ds.data_ptr(), _lib.ptr(dw), rows, D, s.stride(0), dy2.stride(0),
+                                           0 if dr2 is None else dr2.stride(0), ds.stride(0),
+                                           _lib.dtype_code(s.dtype), _lib.dtype_code(y_dtype),
+                                           _lib.current_stream(s.device))
+        _lib.check(rc, "mb200_add_rmsnorm_bwd")
+        ds = ds.view(shape)
+        return ds.to(tx), None if tr is None else ds.to(tr), None if dw is None else dw.to(tw), None, None
+
+
+def add_rms_norm(x, residual=None, weight=None, eps=1e-5):
+    """s = x + residual (residual None: s = x); y = RMSNorm(s).  Returns (y, s) from ONE pass over the data:
+    the residual add of one layer fused with the normalisation in front of the next
+    (mambapy/mamba.py:106-112).  Under autocast y comes out in the autocast dtype, which is what the
+    projection that consumes it would cast it to anyway."""
+    if not x.is_cuda:
+        raise RuntimeError("mamba_b200 kernels need CUDA tensors; there is no CPU path")
+    y_dtype = x.dtype if residual is None else torch.promote_types(x.dtype, residual.dtype)
+    if torch.is_autocast_enabled():
+        y_dtype = torch.get_autocast_gpu_dtype()
+    if y_dtype not in (torch.float32, torch.bfloat16):
+        y_dtype = torch.float32
+    return AddRMSNormFn.apply(x, residual, weight, eps, y_dtype)
+
+
+def stack_forward(self, x):
+    """Drop-in for Mamba.forward (mambapy/mamba.py:77-85): the loop over ResidualBlocks
+    (`x = mixer(norm(x)) + x`, mambapy/mamba.py:106-112) with each layer's residual add fused into the
+    next layer's RMSNorm; the last add stays an ordinary add."""
+    h, res = x, None
+    for layer in self.layers:
+        norm = layer.norm
+        normed, res = add_rms_norm(h, res, None if getattr(norm, "use_mup", False) else norm.weight, norm.eps)
+        h = layer.mixer(normed)
+    return h + res if res is not None else h
+
+
 def rmsnorm_forward(self, x):
     """Drop-in for RMSNorm.forward (mambapy/mamba.py:427-433)."""
     return rms_norm(x, None if getattr(self, "use_mup", False) else self.weight, self.eps)
@@ -335,6 +429,69 @@ def step(self, x, cache):
     return self.out_proj(y), (h, inputs)
 
 
+class FusedInnerFn(torch.autograd.Function):
+    """Everything between in_proj and out_proj of MambaBlock.forward (mambapy/mamba.py:214-231) as ONE autograd
+    node: conv1d + SiLU, x_proj, dt_proj, and the fused scan with softplus(delta + bias) and the gate inside.
+
+    Written as separate nodes, autograd glues the backward together with copies: a `cat` of the gradients of
+    the two halves of xz (the whole (B, L, 2*ED) tensor again), a `cat` for the split of the x_proj output, an
+    add of the two gradients that reach the conv output, and casts of dB, dC.  Here the backward writes dz and
+    the conv's dx straight into the two halves of d(xz), dB and dC straight into d(x_proj output), and adds
+    the second gradient of the conv output in the epilogue of the GEMM that produces it."""
+
+    @staticmethod
+    def forward(ctx, xz, conv_w, conv_b, xproj_w, dt_w, dt_b, A_log, D, dt_rank, d_state):
+        dt = xz.dtype
+        ED = xz.shape[-1] // 2
+        R, N = dt_rank, d_state
+        xs, z = xz[..., :ED], xz[..., ED:]
+        cw32 = conv_w.detach().reshape(ED, conv_w.shape[-1]).float().contiguous()
+        cb32 = _f32(conv_b)
+        xc = conv1d_silu_fwd_raw(xs, cw32, cb32)
+        Wx, Wdt = xproj_w.detach().to(dt), dt_w.detach().to(dt)
+        dbc = F.linear(xc, Wx)                                   # (B, L, R + 2N)
+        delta_r = F.linear(dbc[..., :R], Wdt)                    # (B, L, ED); bias and softplus happen in the kernel
+        A = -torch.exp(A_log.detach().float())
+        D32, b32 = _f32(D), _f32(dt_b)
+        needs_grad = any(ctx.needs_input_grad)
+        y, _, carries = sscan_fwd_raw(xc, delta_r, A, dbc[..., R:R + N], dbc[..., R + N:], D32, z, b32,
+                                      want_carries=needs_grad)
+        ctx.save_for_backward(xz, xc, dbc, delta_r, A, D32, b32, carries, cw32, cb32, Wx, Wdt)
+        ctx.meta = (R, N, conv_w.shape, conv_w.dtype, None if conv_b is None else conv_b.dtype, xproj_w.dtype,
+                    dt_w.dtype, dt_b.dtype, A_log.dtype, D.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xz, xc, dbc, delta_r, A, D32, b32, carries, cw32, cb32, Wx, Wdt = ctx.saved_tensors
+        R, N, cw_shape, t_cw, t_cb, t_wx, t_wdt, t_bdt, t_A, t_D = ctx.meta
+        ED = xc.shape[-1]
+        dy = _rows(dy, xc.dtype)
+        dxz = torch.empty_like(xz, memory_format=torch.contiguous_format)
+        dx_s, dd, _, dB, dC, dA, dD, dbias, _ = sscan_bwd_raw(
+            xc, delta_r, A, dbc[..., R:R + N], dbc[..., R + N:], D32, xz[..., ED:], b32, dy, carries,
+            out_dz=dxz[..., ED:])
+        d_dbc = torch.empty_like(dbc)
+        dd2 = dd.flatten(0, 1)
+        d_dbc[..., :R] = F.linear(dd, Wdt.t())                   # through dt_proj
+        d_dbc[..., R:R + N].copy_(dB)                            # float32 accumulators -> activation dtype, in place
+        d_dbc[..., R + N:].copy_(dC)
+        d2 = d_dbc.flatten(0, 1)
+        dWdt = dd2.t() @ dbc[..., :R].flatten(0, 1)              # (ED, R)
+        dWx = d2.t() @ xc.flatten(0, 1)                          # (R + 2N, ED)
+        dx_s.flatten(0, 1).addmm_(d2, Wx)                        # + gradient through x_proj, in the GEMM's epilogue
+        _, dcw, dcb = conv1d_silu_bwd_raw(xz[..., :ED], cw32, cb32, dx_s, out_dx=dxz[..., :ED])
+        return (dxz, dcw.reshape(cw_shape).to(t_cw), None if dcb is None else dcb.to(t_cb), dWx.to(t_wx), dWdt.to(t_wdt),
+                dbias.to(t_bdt), (dA * A).to(t_A), dD.to(t_D), None, None)
+
+
+def _fusable(self, xz):
+    cfg = self.config
+    return (xz.is_cuda and xz.dtype in (torch.float32, torch.bfloat16) and self.conv1d.weight.shape[-1] == 4
+            and getattr(self, "dt_layernorm", None) is None and getattr(self, "B_layernorm", None) is None
+            and getattr(self, "C_layernorm", None) is None and cfg.d_state in (8, 16, 32, 64))
+
+
 def ssm(self, x, z):
     """mambapy/mamba.py:236-272 with softplus(delta + dt_bias), the scan and the gate fused.
 
@@ -350,6 +507,11 @@ def forward(self, x):
     """mambapy/mamba.py:205-234 with the scan path fused; x: (B, L, D) -> (B, L, D)."""
     _, L, _ = x.shape
     xz = self.in_proj(x)
+    if _fusable(self, xz):
+        cfg = self.config
+        y = FusedInnerFn.apply(xz, self.conv1d.weight, self.conv1d.bias, self.x_proj.weight, self.dt_proj.weight,
+                               self.dt_proj.bias, self.A_log, self.D, cfg.dt_rank, cfg.d_state)
+        return self.out_proj(y)
     xs, z = xz.chunk(2, dim=-1)
     if self.conv1d.weight.shape[-1] == 4:
         xs = causal_conv1d_silu(xs, self.conv1d.weight, self.conv1d.bias)

@@ -36,7 +36,8 @@ def install(fuse_block: bool = False) -> None:
     fuse_block=False keeps MambaBlock.forward/ssm as they are and swaps only the methods whose
     signatures the reference defines (selective_scan, selective_scan_seq, ssm_step, step) plus
     pscan/PScan.  fuse_block=True also swaps MambaBlock.ssm and MambaBlock.forward for the
-    variants that run softplus, scan and gate in one kernel, RMSNorm.forward for the one-pass kernel,
+    variants that run softplus, scan and gate in one kernel, Mamba.forward for a loop that fuses each
+    layer's residual add into the next layer's RMSNorm, RMSNorm.forward for the one-pass kernel,
     and (when mambapy.vim has been imported) the bidirectional block's forward (mambapy/vim.py:205-261)
     for one that scans the second direction in place instead of flipping the sequence.
     """
@@ -64,6 +65,9 @@ def install(fuse_block: bool = False) -> None:
     if fuse_block:
         _swap(blocks[0], "ssm", _m.ssm)
         _swap(blocks[0], "forward", _m.forward)
+        stack = getattr(sys.modules["mambapy.mamba"], "Mamba", None)
+        if stack is not None:
+            _swap(stack, "forward", _m.stack_forward)     # residual adds fused into the following RMSNorm
         for modname in ("mambapy.mamba", "mambapy.vim"):
             norm = getattr(sys.modules.get(modname), "RMSNorm", None)
             if norm is not None:

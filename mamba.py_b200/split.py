@@ -39,7 +39,8 @@ class CudaOps:
 
     @staticmethod
     def carry_pass(x, delta, A, Bm, Cm, delta_bias):
-        """-> (state reached from zero, decay product), each (rows, ED, N)."""
+        """-> one (2, rows, ED, N) tensor: [0] the decay product of every row's span, [1] the state it reaches
+        from a zero state."""
         return sscan_fwd_carry_raw(x, delta, A, Bm, delta_bias)
 
     @staticmethod
@@ -104,12 +105,16 @@ def pick_subshards(Bsz, L_local, ED, world=1):
     def cost(S):
         c = items * S / 148.0                                # CTAs per SM
         f = 1.0 if c <= 1 else (1 + 0.415 * (c - 1) if c <= 3 else 1.83 * c / 3)
-        extra = 1.6 if (world == 1 and S > 1) else 1.0
+        extra = 1.3 if (world == 1 and S > 1) else 1.0       # carry passes: +35 % of a forward, +20 % of a backward
         return (L_local / S) * f * extra
 
+    # Below a few thousand timesteps a step is a fraction of a millisecond and the four extra launches of a
+    # cut (and their host-side cost) eat what it gains.
+    if world == 1 and L_local < 4096:
+        return 1
     best, best_cost = 1, cost(1)
     for S in (2, 4, 8, 16):
-        if L_local % (16 * S) or L_local // S < 128:
+        if L_local % (16 * S) or L_local // S < 256:
             continue
         if cost(S) < best_cost * 0.9:                        # a cut has to pay for its extra launches
             best, best_cost = S, cost(S)
@@ -129,10 +134,9 @@ def split_forward(ops, group, x, delta, A, Bm, Cm, D, z, delta_bias, h0=None, wa
     if R * S == 1:
         y, hT, carries = ops.full_fwd(xs, ds, A, Bs, Cs, D, zs, delta_bias, h0, want_carries)
         return y, None, None, carries, hT
-    Sl, P = ops.carry_pass(xs, ds, A, Bs, Cs, delta_bias)                    # (B*S, ED, N) each
-    PS = torch.stack([P, Sl]).unflatten(1, (Bsz, S))                         # (2, B, S, ED, N)
+    PS = ops.carry_pass(xs, ds, A, Bs, Cs, delta_bias).unflatten(1, (Bsz, S))   # (2, B, S, ED, N): decay product, state
     if R > 1:
-        PS = _gather(PS, group).permute(1, 2, 0, 3, 4, 5).reshape(2, Bsz, R * S, *P.shape[1:]).contiguous()
+        PS = _gather(PS, group).permute(1, 2, 0, 3, 4, 5).reshape(2, Bsz, R * S, *PS.shape[3:]).contiguous()
     P_all, S_all = PS[0], PS[1]                                              # (B, R*S, ED, N)
     h_in = ops.fold_range(P_all, S_all, h0, rank * S, S, False).flatten(0, 1)   # (B*S, ED, N)
     y, hT, carries = ops.full_fwd(xs, ds, A, Bs, Cs, D, zs, delta_bias, h_in, want_carries)

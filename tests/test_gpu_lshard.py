@@ -25,8 +25,8 @@ def _emulate(inp, R, dtype, bias=None):
     Ls = L // R
     sl = lambda t, r: t[:, r * Ls:(r + 1) * Ls] if r < R - 1 else t[:, r * Ls:]
     SP = [K.carry_pass(sl(x, r), sl(dl, r), A, sl(Bm, r), sl(Cm, r), b) for r in range(R)]
-    S = torch.stack([sp[0] for sp in SP], dim=1)                    # (B, R, ED, N): state reached from zero
-    P = torch.stack([sp[1] for sp in SP], dim=1)                    # decay product of every shard
+    S = torch.stack([sp[1] for sp in SP], dim=1)                    # (B, R, ED, N): state reached from zero
+    P = torch.stack([sp[0] for sp in SP], dim=1)                    # decay product of every shard
     h_in = K.fold_range(P, S, None, 0, R, False)                    # state entering every shard, one launch
     ys, cars = [], []
     for r in range(R):
@@ -88,8 +88,8 @@ def test_single_rank_subsharded_matches_oracle():
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(_free_port()))
     dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device(DEV))
     try:
-        inp = scan_inputs(91, 1, 512, 64, 16, structured_A=False, big_delta=True)
-        assert pick_subshards(1, 512, 64, 1) > 1
+        inp = scan_inputs(91, 1, 8192, 64, 16, structured_A=False)
+        assert pick_subshards(1, 8192, 64, 1) > 1
         lv = {k: inp[k].to(DEV).requires_grad_() for k in ("x", "delta", "z", "B", "C", "A", "D")}
         y = selective_scan_lsharded(lv["x"], lv["delta"], lv["A"], lv["B"], lv["C"], lv["D"], z=lv["z"])
         y.backward(inp["gy"].to(DEV))

@@ -71,6 +71,8 @@ def test_mamba_forward_backward_and_steps(ref, fuse_block, L):
     want = _fwd_bwd(cpu, x, gy)
     mamba_b200.install(fuse_block=fuse_block)
     assert mamba_b200.installed()
+    if fuse_block:                                   # the layer loop with the residual adds fused into the norms
+        assert rm.Mamba.forward is mamba_b200.mamba.stack_forward
     got = _fwd_bwd(gpu, x.to(DEV), gy.to(DEV))
     _check(got, want, f"fuse_block={fuse_block} L={L}")
     # decode: Mamba.step from (None, zeros) caches (mambapy/mamba.py:87-97, :351-382)

@@ -216,7 +216,7 @@ def test_empty_and_errors():
                                      torch.zeros(1, 4, 16), torch.zeros(1, 4, 16), torch.zeros(8))
 
 
-@pytest.mark.parametrize("Bsz,L,ED,S,use_h0,use_bias", [(1, 1024, 64, None, False, False), (2, 512, 40, 4, True, True),
+@pytest.mark.parametrize("Bsz,L,ED,S,use_h0,use_bias", [(1, 4096, 64, None, False, False), (2, 512, 40, 4, True, True),
                                                        (1, 2048, 96, 16, True, False), (3, 256, 32, 2, False, True)])
 def test_rows_cut_into_pieces_match_the_oracle(Bsz, L, ED, S, use_h0, use_bias):
     """Few batch rows: every row is cut into S pieces scanned side by side (carry pass, fold, full pass, and
