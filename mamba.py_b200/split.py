@@ -95,29 +95,22 @@ def _merge(t, S):
 def pick_subshards(Bsz, L_local, ED, world=1):
     """How many sub-shards to cut each row of this device's slice into.
 
-    The fused kernels have Bsz * ceil(ED / 32) independent work items (a CTA owns one), 148 SMs hold three
-    CTAs each, and an SM's throughput grows with its CTA count (measured forward, one / two / three CTAs per
-    SM: 1 : 1.4 : 1.8 times the single-CTA time for 1 : 2 : 3 times the work).  The model below estimates
-    the time of one pass as (timesteps per piece) x (that factor), plus, on a single rank, the two carry
-    passes a cut adds (about 60 % of a forward each); with several ranks the carry passes exist anyway."""
+    The fused kernels have Bsz * ceil(ED / 32) independent work items (a CTA owns one) and 148 SMs hold three
+    CTAs each.  Measured on B200, forward + backward of one row (ms): ED 2048, L 65536: 12.0 uncut, 7.8 / 5.8 /
+    5.8 / 4.8 in 2 / 4 / 8 / 16 pieces; ED 2048, L 8192: 1.53 uncut, 0.68 in 16; ED 5120, L 131072: 35.5 uncut,
+    27.0 / 23.9 / 23.7 in 4 / 8 / 16.  So: cut until there are about two waves of CTAs (the pieces' tails then
+    overlap), keep pieces at least 512 timesteps long, and leave alone what already fills half the GPU (on a
+    single rank a cut costs two extra carry passes) or is so short that the extra launches eat the gain."""
     items = Bsz * ((ED + 31) // 32)
-
-    def cost(S):
-        c = items * S / 148.0                                # CTAs per SM
-        f = 1.0 if c <= 1 else (1 + 0.415 * (c - 1) if c <= 3 else 1.83 * c / 3)
-        extra = 1.3 if (world == 1 and S > 1) else 1.0       # carry passes: +35 % of a forward, +20 % of a backward
-        return (L_local / S) * f * extra
-
-    # Below a few thousand timesteps a step is a fraction of a millisecond and the four extra launches of a
-    # cut (and their host-side cost) eat what it gains.
-    if world == 1 and L_local < 4096:
+    if world == 1 and (L_local < 4096 or 2 * items >= RESIDENT_CTAS):
         return 1
-    best, best_cost = 1, cost(1)
+    best = 1
     for S in (2, 4, 8, 16):
-        if L_local % (16 * S) or L_local // S < 256:
-            continue
-        if cost(S) < best_cost * 0.9:                        # a cut has to pay for its extra launches
-            best, best_cost = S, cost(S)
+        if L_local % (16 * S) or L_local // S < 512:
+            break
+        best = S
+        if items * S >= 2 * RESIDENT_CTAS:
+            break
     return best
 
 

@@ -129,7 +129,9 @@ def test_two_cpu_ranks_reproduce_the_single_sequence(use_bias, S):
 def test_pick_subshards():
     from mamba_b200.lshard import pick_subshards
     assert pick_subshards(8, 2048, 1536, 1) == 1            # already enough rows x channel tiles
-    assert pick_subshards(1, 65536, 2048, 1) == 8           # one long row of a 1024-wide model: cut it up
+    assert pick_subshards(1, 65536, 2048, 1) == 16          # one long row of a 1024-wide model: cut it up
+    assert pick_subshards(1, 131072, 5120, 1) == 8          # about two waves of CTAs are enough
     assert pick_subshards(1, 16384, 5120, 8) > 1            # several ranks: the carry passes exist anyway
     assert pick_subshards(1, 40, 5120, 1) == 1              # not divisible into 16-step pieces
     assert pick_subshards(1, 2048, 2048, 1) == 1            # short: the extra launches would eat the gain
+    assert pick_subshards(1, 4096, 64, 1) == 8              # pieces stay at least 512 timesteps long
