@@ -346,6 +346,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--skip-e2e", action="store_true", help="profiling runs: leave out the host-buffer leg")
     ap.add_argument("--decode-layers", type=int, default=64, help="layers of the decode workload")
+    ap.add_argument("--pscan-batch", type=int, default=16, help="batch rows of the pscan workload (16 = the configuration; smaller for profiler captures)")
     ap.add_argument("--lshard-len", type=int, default=131072, help="sequence length of the lshard workload")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -384,6 +385,9 @@ def main():
         "roofline": roofline_of(res, peaks, peak_kind), "kernels": res.get("kernels"),
         "e2e": res.get("e2e"), "gpu_launches": res["gpu_launches"], "clocks": res.get("clocks"),
     }
+    if wl == "pscan" and args.pscan_batch != 16:
+        line["config"].update(B_per_gpu=args.pscan_batch, global_batch=args.pscan_batch * world,
+                              l2="reduced batch (profiler capture), still larger than L2")
     if extras:
         # the sequence-sharded scan at every N (its parity self-check first), then the single-GPU summaries
         line["lshard_parity"] = legs.lshard_parity(rank, world, dev)

@@ -613,7 +613,7 @@ def bench_scan_130m(args, rank, world, dev, T, summary=False):
 def bench_pscan(args, rank, world, dev, T, summary=False):
     import mamba_b200
     from mamba_b200.pscan import pscan_fwd_raw, pscan_bwd_raw
-    Bsz, L, D, N = 16, 2048, 1536, 16
+    Bsz, L, D, N = getattr(args, "pscan_batch", 16), 2048, 1536, 16
     A, X, G = workloads.pscan_inputs(1001 + rank, dev, Bsz, L, D, N)
     A.requires_grad_()
     X.requires_grad_()

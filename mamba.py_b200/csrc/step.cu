@@ -13,6 +13,13 @@ namespace {
 
 constexpr int kStepThreads = 256;
 
+// States per lane.  The work per (batch row, channel) - softplus, the gate, index arithmetic - is repeated
+// by every lane of the channel, and the kernel is bound as much by instruction issue as by memory, so
+// a lane takes MB200_STEP_SPL consecutive states (N / SPL lanes share a channel).
+#ifndef MB200_STEP_SPL
+#define MB200_STEP_SPL 8
+#endif
+
 template <typename T, int N, bool kVecBC>
 __global__ void __launch_bounds__(kStepThreads)
 ssm_step_kernel(const T* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ z,
@@ -21,8 +28,10 @@ ssm_step_kernel(const T* __restrict__ x, const T* __restrict__ delta, const T* _
                 const float* __restrict__ h_in, float* __restrict__ h_out, T* __restrict__ y,
                 int64_t ED, int64_t x_sb, int64_t d_sb, int64_t z_sb, int64_t b_sb,
                 int64_t c_sb, int64_t y_sb, int flags) {
-  constexpr int kLPE = N / 4;
-  constexpr int kEPB = kStepThreads / kLPE;          // channels per CTA
+  constexpr int kSPL = MB200_STEP_SPL < N ? MB200_STEP_SPL : N;   // states per lane
+  constexpr int kV = kSPL / 4;                                    // float4 per lane
+  constexpr int kLPE = N / kSPL;                                  // lanes per channel
+  constexpr int kEPB = kStepThreads / kLPE;                       // channels per CTA
   const int tid = threadIdx.x;
   const int q = tid % kLPE;
   const int64_t e = int64_t(blockIdx.x) * kEPB + tid / kLPE;
@@ -31,36 +40,48 @@ ssm_step_kernel(const T* __restrict__ x, const T* __restrict__ delta, const T* _
   float yv = 0.f, xv = 0.f;
   if (ok) {
     // the state is the only large stream: get it moving first, everything else is small
-    float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (h_in) hv = __ldcs(reinterpret_cast<const float4*>(h_in + (b * ED + e) * N + 4 * q));
-    const float4 Av = *reinterpret_cast<const float4*>(A + e * N + 4 * q);
-    float b4[4], c4[4];
-    if constexpr (kVecBC) {
-      const Vec4<T> bv = *reinterpret_cast<const Vec4<T>*>(Bm + b * b_sb + 4 * q);
-      const Vec4<T> cv = *reinterpret_cast<const Vec4<T>*>(Cm + b * c_sb + 4 * q);
+    float4 hv[kV];
+    const float4* hp = reinterpret_cast<const float4*>(h_in + (b * ED + e) * N + kSPL * q);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { b4[j] = Elem<T>::to_f(bv.v[j]); c4[j] = Elem<T>::to_f(cv.v[j]); }
+    for (int v = 0; v < kV; ++v) hv[v] = h_in ? __ldcs(hp + v) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 Av[kV];
+#pragma unroll
+    for (int v = 0; v < kV; ++v) Av[v] = *reinterpret_cast<const float4*>(A + e * N + kSPL * q + 4 * v);
+    float b4[kSPL], c4[kSPL];
+    if constexpr (kVecBC) {
+#pragma unroll
+      for (int v = 0; v < kV; ++v) {
+        const Vec4<T> bv = *reinterpret_cast<const Vec4<T>*>(Bm + b * b_sb + kSPL * q + 4 * v);
+        const Vec4<T> cv = *reinterpret_cast<const Vec4<T>*>(Cm + b * c_sb + kSPL * q + 4 * v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { b4[4 * v + j] = Elem<T>::to_f(bv.v[j]); c4[4 * v + j] = Elem<T>::to_f(cv.v[j]); }
+      }
     } else {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        b4[j] = Elem<T>::to_f(Bm[b * b_sb + 4 * q + j]);
-        c4[j] = Elem<T>::to_f(Cm[b * c_sb + 4 * q + j]);
+      for (int j = 0; j < kSPL; ++j) {
+        b4[j] = Elem<T>::to_f(Bm[b * b_sb + kSPL * q + j]);
+        c4[j] = Elem<T>::to_f(Cm[b * c_sb + kSPL * q + j]);
       }
     }
     xv = Elem<T>::to_f(x[b * x_sb + e]);
     float dv = Elem<T>::to_f(delta[b * d_sb + e]);
     if (flags & MB200_DELTA_SOFTPLUS) dv = softplus_fast(dv + delta_bias[e]);
-    const float a4[4] = {Av.x, Av.y, Av.z, Av.w};
-    float h4[4] = {hv.x, hv.y, hv.z, hv.w};
-    const float dx = dv * xv, d2 = dv * kLog2e;
+    const float dxs = dv * xv, d2s = dv * kLog2e;
+    const float2 dx = make_float2(dxs, dxs), d2 = make_float2(d2s, d2s);
+    float2 y2 = make_float2(0.f, 0.f);
+    float4* op = reinterpret_cast<float4*>(h_out + (b * ED + e) * N + kSPL * q);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float a = ex2f(d2 * a4[j]);
-      h4[j] = fmaf(a, h4[j], dx * b4[j]);
-      yv = fmaf(h4[j], c4[j], yv);
+    for (int v = 0; v < kV; ++v) {
+      // packed f32x2 arithmetic: two states per instruction (the decays stay scalar ex2)
+      const float2 e01 = __fmul2_rn(d2, make_float2(Av[v].x, Av[v].y)), e23 = __fmul2_rn(d2, make_float2(Av[v].z, Av[v].w));
+      const float2 a01 = make_float2(ex2f(e01.x), ex2f(e01.y)), a23 = make_float2(ex2f(e23.x), ex2f(e23.y));
+      const float2 h01 = __ffma2_rn(a01, make_float2(hv[v].x, hv[v].y), __fmul2_rn(dx, make_float2(b4[4 * v], b4[4 * v + 1])));
+      const float2 h23 = __ffma2_rn(a23, make_float2(hv[v].z, hv[v].w), __fmul2_rn(dx, make_float2(b4[4 * v + 2], b4[4 * v + 3])));
+      y2 = __ffma2_rn(h01, make_float2(c4[4 * v], c4[4 * v + 1]), y2);
+      y2 = __ffma2_rn(h23, make_float2(c4[4 * v + 2], c4[4 * v + 3]), y2);
+      __stcs(op + v, make_float4(h01.x, h01.y, h23.x, h23.y));
     }
-    __stcs(reinterpret_cast<float4*>(h_out + (b * ED + e) * N + 4 * q),
-           make_float4(h4[0], h4[1], h4[2], h4[3]));
+    yv = y2.x + y2.y;
   }
 #pragma unroll
   for (int s = kLPE / 2; s >= 1; s >>= 1) yv += __shfl_xor_sync(0xffffffffu, yv, s);
@@ -218,7 +239,7 @@ static int ssm_step_t(const void* x, const void* delta, const void* z, const flo
                       (reinterpret_cast<uintptr_t>(Cm) % (4 * sizeof(T)) == 0) && b_sb % 4 == 0 && c_sb % 4 == 0;
 #define MB200_STEP(NN)                                                                          \
   {                                                                                             \
-    constexpr int epb = kStepThreads / (NN / 4);                                                \
+    constexpr int epb = kStepThreads / (NN / (MB200_STEP_SPL < NN ? MB200_STEP_SPL : NN));      \
     dim3 grid(unsigned((ED + epb - 1) / epb), unsigned(B));                                     \
     if (vec_bc)                                                                                 \
       ssm_step_kernel<T, NN, true><<<grid, kStepThreads, 0, st>>>(                              \
