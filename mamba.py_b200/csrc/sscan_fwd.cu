@@ -198,7 +198,11 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
 
   if (tid < kNC) {
     // ------------------------------------------------------------------ consumers
-    const int grp = tid / kLPE, q = tid % kLPE;        // channel group (kCPT channels) and state quad
+    // One channel per thread: the lanes of a warp are neighbouring CHANNELS with the same state quad q, so
+    // the warp's B and C loads have a single address.  Shared memory delivers a 16-byte load with four
+    // distinct addresses (lanes = 8 channels x 4 quads) in 4 wavefronts, one with a single address in 2.
+    const int grp = (kCPT == 1) ? tid % kTE : tid / kLPE;
+    const int q = (kCPT == 1) ? tid / kTE : tid % kLPE;   // state quad
     const int e_l = grp * kCPT;                        // first channel of this thread inside the tile
     float2 A2lo[kCPT], A2hi[kCPT], hlo[kCPT], hhi[kCPT];
     float A0[kCPT];
@@ -224,8 +228,7 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
     // where this thread leaves its partial C-contractions inside a timestep's row of partial sums
     int yp_off0, yp_off1;
     if constexpr (kCPT == 1) {
-      yp_off0 = yp_slot<kLPE, kTE>(0, e_l) * kLPE + q;
-      yp_off1 = yp_slot<kLPE, kTE>(1, e_l) * kLPE + q;
+      yp_off0 = yp_off1 = q * kTE + e_l;                          // [quad][channel]: a warp stores one contiguous row
     } else {
       yp_off0 = yp_off1 = ((e_l >> 2) * 4 + q) * 4 + (e_l & 3);   // [channel quad][q][channel in quad]
     }
@@ -479,9 +482,15 @@ sscan_fwd_tma_kernel(const __grid_constant__ FwdMaps maps, const SscanFwdParams 
         const int ps = rev ? kTile - 1 - rr : rr;            // processing step that produced row rr
         float s4[4];
         if constexpr (kCPT == 1) {
+          // one 16-byte vector per state quad holds that quad's partial sums of channels cc .. cc+3
+          const float4* quad = reinterpret_cast<const float4*>(yp + ps * kYpRow + cc);
+          float4 acc = quad[0];
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            s4[k] = sum_lanes<kLPE>(yp + ps * kYpRow + yp_slot<kLPE, kTE>(ps, cc + k) * kLPE);
+          for (int j = 1; j < kLPE; ++j) {
+            const float4 w = quad[j * (kTE / 4)];
+            acc.x += w.x; acc.y += w.y; acc.z += w.z; acc.w += w.w;
+          }
+          s4[0] = acc.x; s4[1] = acc.y; s4[2] = acc.z; s4[3] = acc.w;
         } else {
           // the four state quads' partials of channels cc .. cc+3 are four 16-byte vectors; lanes start at
           // different ones so that a quarter-warp's loads fall into different banks
