@@ -12,16 +12,18 @@
 //
 // Structure (this file, used whenever the tensors satisfy the tensor-map alignment rules;
 // sscan_fwd_generic.cuh holds the register-staged path for everything else):
-// a CTA of 256 threads owns a tile of channels of one batch row and walks time in tiles of 16.
-//   - One thread issues TMA loads (cp.async.bulk.tensor, 3-D maps {channels, L, B}) of the raw
-//     x, delta, z, B, C boxes two tiles ahead into a 4-stage shared-memory ring; ragged L and
-//     ragged channel tiles are zero-filled by the copy engine.
+// a CTA of 288 threads owns a tile of 32 channels (d_state 16) of one batch row and walks time in tiles of 16.
+//   - One warp does nothing but issue TMA loads (cp.async.bulk.tensor, 3-D maps {channels, L, B}) of the
+//     raw x, delta, z, B, C boxes into a shared-memory ring, as far ahead as the ring has free stages;
+//     ragged L and ragged channel tiles are zero-filled by the copy engine.
 //   - 4 producer warps turn a raw tile into float32 operands ({softplus(delta+bias), delta*x},
 //     B, C; swizzled, double-buffered) and, two tiles later, finish it: sum the N/4 partial
 //     C-contractions per channel, add D*x, apply the SiLU(z) gate, store y.
-//   - 4 consumer warps run nothing but the recurrence: a thread owns 4 consecutive states of one
-//     channel; per timestep 3 shared loads, 4 ex2, 8 packed f32x2 operations and one 4-byte
-//     store of its partial C-contraction.
+//   - 4 recurrence warps run nothing but the recurrence: a thread owns 4 consecutive states of one
+//     channel, a warp the same 4 states of 32 neighbouring channels; per timestep 3 shared loads, 4 ex2
+//     (2 when A has the S4D-real structure), 8 packed f32x2 operations and one 4-byte store of its partial
+//     C-contraction, with the loads and decays of later timesteps written next to the recurrence of
+//     the current one (the warp issues in order).
 //   - Hand-off through CTA-local mbarriers.  Every wait is bounded: a wait that gives up records
 //     MB200_DEV_WAIT_TIMEOUT and the thread leaves the kernel, so nothing can spin forever.
 #include <type_traits>
