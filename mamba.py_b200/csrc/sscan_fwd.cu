@@ -4,11 +4,12 @@
 //
 // What bounds it.  Per (b, t, e, n) element the kernel needs one ex2 (16/clk/SM on the MUFU
 // pipe), four FP32 operations, and its B and C operands out of shared memory; HBM traffic is
-// 0.5 byte per element.  Measured on B200 the recurrence loop alone runs at the shared-memory
-// return bandwidth (128 B/clk/SM), ahead of the MUFU pipe and far ahead of HBM, and the
-// per-(t, e) work around it (softplus, delta*x, D skip, gate, conversions) is 70 % as many
-// instructions again.  So: no redundant arithmetic (every recurrence is walked serially along L
-// by exactly one thread), and everything that is not the recurrence runs on other warps.
+// 0.5 byte per element.  Measured on B200 no single unit is the limit (shared-memory pipe ~75 %, issue
+// ~65 %, FMA ~40 %, MUFU ~38 %, DRAM ~20 %): the time is that of the in-order recurrence warps, whose
+// dependent chain only overlaps with the other resident warps.  So: no redundant arithmetic (every
+// recurrence is walked serially along L by exactly one thread), everything that is not the recurrence
+// (softplus, delta*x, D skip, gate, conversions: 70 % as many instructions again) runs on other warps,
+// and the recurrence is software-pipelined by hand.
 //
 // Structure (this file, used whenever the tensors satisfy the tensor-map alignment rules;
 // sscan_fwd_generic.cuh holds the register-staged path for everything else):
