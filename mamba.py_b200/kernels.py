@@ -128,14 +128,19 @@ def sscan_bwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in=None,
 
 
 
-def sscan_fwd_carry_raw(x, delta, A, Bm, delta_bias=None):
+def sscan_fwd_carry_raw(x, delta, A, Bm, delta_bias=None, skip_last=0):
     """Forward carry pass of a span, one pass over x, delta, B.  Returns one (2, B, ED, N) float32 tensor:
-    [0] the span's decay product exp(A * sum_t delta), [1] the state reached from a zero state."""
+    [0] the span's decay product exp(A * sum_t delta), [1] the state reached from a zero state.
+    The last `skip_last` rows are not scanned (their entries are zero): nothing follows the last piece of
+    a sequence, so its carry is never used."""
     lib = _lib.load()
-    Bsz, L, ED = x.shape
+    rows, L, ED = x.shape
+    Bsz = rows - skip_last
     N = A.shape[1]
     dev = x.device
-    out = torch.empty((2, Bsz, ED, N), dtype=torch.float32, device=dev)
+    out = torch.empty((2, rows, ED, N), dtype=torch.float32, device=dev)
+    if skip_last:
+        out[:, Bsz:].zero_()
     flags = _lib.DELTA_SOFTPLUS if delta_bias is not None else 0
     with torch.cuda.device(dev):
         rc = lib.mb200_sscan_fwd_carry(x.data_ptr(), delta.data_ptr(), A.data_ptr(), Bm.data_ptr(), _lib.ptr(delta_bias),
@@ -147,13 +152,20 @@ def sscan_fwd_carry_raw(x, delta, A, Bm, delta_bias=None):
     return out
 
 
-def sscan_bwd_carry_raw(delta, z, dy, Cm, A, delta_bias=None):
+def sscan_bwd_carry_raw(delta, z, dy, Cm, A, delta_bias=None, skip_first=0):
     """Reverse carry pass of a span: the gradient carry (B, ED, N) float32 that leaves its first timestep
-    when none enters its last one."""
+    when none enters its last one.  The first `skip_first` rows are not scanned (entries zero): nothing
+    precedes the first piece of a sequence."""
     lib = _lib.load()
-    Bsz, L, ED = delta.shape
+    rows, L, ED = delta.shape
     N = A.shape[1]
-    g = torch.empty((Bsz, ED, N), dtype=torch.float32, device=delta.device)
+    g_all = torch.empty((rows, ED, N), dtype=torch.float32, device=delta.device)
+    if skip_first:
+        g_all[:skip_first].zero_()
+        delta, dy, Cm = delta[skip_first:], dy[skip_first:], Cm[skip_first:]
+        z = z[skip_first:] if z is not None else None
+    g = g_all[skip_first:]
+    Bsz = rows - skip_first
     flags = _lib.DELTA_SOFTPLUS if delta_bias is not None else 0
     zs = (z.stride(0), z.stride(1)) if z is not None else (0, 0)
     with torch.cuda.device(delta.device):
@@ -164,7 +176,7 @@ def sscan_bwd_carry_raw(delta, z, dy, Cm, A, delta_bias=None):
             _lib.dtype_code(delta.dtype), flags, _lib.current_stream(delta.device))
     _lib.check(rc, "mb200_sscan_bwd_carry")
     _lib.check_status(delta.device, "mb200_sscan_bwd_carry")
-    return g
+    return g_all
 
 
 def carry_fold_range(P_all, S_all, init, first, num, reverse):

@@ -38,10 +38,10 @@ class CudaOps:
     """The piece-local arithmetic, every method one kernel launch of libmamba_b200.so."""
 
     @staticmethod
-    def carry_pass(x, delta, A, Bm, Cm, delta_bias):
+    def carry_pass(x, delta, A, Bm, Cm, delta_bias, skip_last=0):
         """-> one (2, rows, ED, N) tensor: [0] the decay product of every row's span, [1] the state it reaches
-        from a zero state."""
-        return sscan_fwd_carry_raw(x, delta, A, Bm, delta_bias)
+        from a zero state.  The last `skip_last` rows are left out (zeros)."""
+        return sscan_fwd_carry_raw(x, delta, A, Bm, delta_bias, skip_last=skip_last)
 
     @staticmethod
     def fold_range(P_all, S_all, init, first, num, reverse):
@@ -53,8 +53,8 @@ class CudaOps:
         return sscan_fwd_raw(x, delta, A, Bm, Cm, D, z, delta_bias, h_in, want_last=True, want_carries=want_carries)
 
     @staticmethod
-    def rev_carry_pass(delta, z, dy, Cm, A, delta_bias):
-        return sscan_bwd_carry_raw(delta, z, dy, Cm, A, delta_bias)
+    def rev_carry_pass(delta, z, dy, Cm, A, delta_bias, skip_first=0):
+        return sscan_bwd_carry_raw(delta, z, dy, Cm, A, delta_bias, skip_first=skip_first)
 
     @staticmethod
     def full_bwd(x, delta, A, Bm, Cm, D, z, delta_bias, dy, carries, g_in):
@@ -127,7 +127,10 @@ def split_forward(ops, group, x, delta, A, Bm, Cm, D, z, delta_bias, h0=None, wa
     if R * S == 1:
         y, hT, carries = ops.full_fwd(xs, ds, A, Bs, Cs, D, zs, delta_bias, h0, want_carries)
         return y, None, None, carries, hT
-    PS = ops.carry_pass(xs, ds, A, Bs, Cs, delta_bias).unflatten(1, (Bsz, S))   # (2, B, S, ED, N): decay product, state
+    # one row on one rank: its last piece's carry feeds nothing, so that piece is left out of the pass
+    skip = 1 if (R == 1 and Bsz == 1) else 0
+    PS = ops.carry_pass(xs, ds, A, Bs, Cs, delta_bias, **({"skip_last": 1} if skip else {}))
+    PS = PS.unflatten(1, (Bsz, S))                                          # (2, B, S, ED, N): decay product, state
     if R > 1:
         PS = _gather(PS, group).permute(1, 2, 0, 3, 4, 5).reshape(2, Bsz, R * S, *PS.shape[3:]).contiguous()
     P_all, S_all = PS[0], PS[1]                                              # (B, R*S, ED, N)
@@ -147,7 +150,9 @@ def split_backward(ops, group, x, delta, A, Bm, Cm, D, z, delta_bias, dy, carrie
     if R * S == 1:
         g_in = None
     else:
-        G = ops.rev_carry_pass(ds, zs, dys, Cs, A, delta_bias).unflatten(0, (Bsz, S))     # (B, S, ED, N)
+        skip = 1 if (R == 1 and Bsz == 1) else 0                    # the first piece's carry feeds nothing
+        G = ops.rev_carry_pass(ds, zs, dys, Cs, A, delta_bias, **({"skip_first": 1} if skip else {}))
+        G = G.unflatten(0, (Bsz, S))                                                      # (B, S, ED, N)
         if R > 1:
             G = _gather(G, group).permute(1, 0, 2, 3, 4).reshape(Bsz, R * S, *G.shape[2:])
         g_in = ops.fold_range(P_all, G.contiguous(), None, rank * S, S, True).flatten(0, 1)

@@ -20,10 +20,13 @@ class OracleOps:
         return delta if bias is None else torch.nn.functional.softplus(delta + bias)
 
     @staticmethod
-    def carry_pass(x, delta, A, Bm, Cm, bias):
+    def carry_pass(x, delta, A, Bm, Cm, bias, skip_last=0):
         d = OracleOps._delta(delta, bias)
         _, h = O.selective_scan_f64(x, d, A, Bm, Cm, torch.zeros(x.shape[2]), return_last_state=True)
-        return torch.stack([torch.exp(d.double().sum(1).unsqueeze(-1) * A.double()), h])
+        out = torch.stack([torch.exp(d.double().sum(1).unsqueeze(-1) * A.double()), h])
+        if skip_last:                      # the product leaves these rows out of the pass and returns zeros
+            out[:, out.shape[1] - skip_last:] = 0
+        return out
 
     @staticmethod
     def fold_range(P_all, S_all, init, first, num, reverse):
@@ -44,14 +47,17 @@ class OracleOps:
         return y, hT, h_in          # the "carries" of the stand-in are just the incoming state
 
     @staticmethod
-    def rev_carry_pass(delta, z, dy, Cm, A, bias):
+    def rev_carry_pass(delta, z, dy, Cm, A, bias, skip_first=0):
         Bsz, L, ED = delta.shape
         h0 = torch.zeros(Bsz, ED, A.shape[1], dtype=torch.float64, requires_grad=True)
         x0 = torch.zeros(Bsz, L, ED, dtype=torch.float64)
         y = O.selective_scan_f64(x0, OracleOps._delta(delta, bias), A, torch.zeros_like(Cm), Cm,
                                  torch.zeros(ED), z=z, h0=h0)
         y.backward(dy.double())
-        return h0.grad
+        g = h0.grad
+        if skip_first:
+            g[:skip_first] = 0
+        return g
 
     @staticmethod
     def full_bwd(x, delta, A, Bm, Cm, D, z, bias, dy, carries, g_in):
@@ -124,6 +130,47 @@ def test_two_cpu_ranks_reproduce_the_single_sequence(use_bias, S):
             assert torch.allclose(out[r]["grads"][7], bl.grad, **tol)
     # the carry leaving rank 0 to the left is the gradient w.r.t. a (zero) initial state
     assert out[0]["grads"][8].shape == (2, 6, 8)
+
+
+def test_one_row_cut_on_one_rank_leaves_out_the_unused_carries():
+    """Single rank, single batch row: the forward carry pass leaves out the last piece and the reverse one
+    the first piece (nothing consumes their carries); the result must still be the uncut scan."""
+    from mamba_b200 import split
+    inp = scan_inputs(78, 1, 64, 6, 8, structured_A=False, big_delta=True)
+    g = torch.Generator().manual_seed(6)
+    bias = torch.randn(6, generator=g) - 1.0
+    inp["delta"] = torch.randn(1, 64, 6, generator=g)
+    h0 = torch.randn(1, 6, 8, generator=g).double()
+    args = (inp["x"].double(), inp["delta"].double(), inp["A"].double(), inp["B"].double(), inp["C"].double(),
+            inp["D"].double(), inp["z"].double(), bias.double())
+    seen = {}
+
+    class Spy(OracleOps):
+        @staticmethod
+        def carry_pass(*a, **k):
+            seen["fwd"] = k
+            return OracleOps.carry_pass(*a, **k)
+
+        @staticmethod
+        def rev_carry_pass(*a, **k):
+            seen["bwd"] = k
+            return OracleOps.rev_carry_pass(*a, **k)
+
+    y, h_in, P_all, carries, hT = split.split_forward(Spy, None, *args, h0=h0, subshards=4)
+    grads = split.split_backward(Spy, None, *args, inp["gy"].double(), h_in, P_all, subshards=4)
+    assert seen == {"fwd": {"skip_last": 1}, "bwd": {"skip_first": 1}}
+    lv = {k: inp[k].double().requires_grad_() for k in ("x", "delta", "z", "B", "C", "A", "D")}
+    bl = bias.double().requires_grad_()
+    h0l = h0.clone().requires_grad_()
+    yr, hTr = O.selective_scan_f64(lv["x"], torch.nn.functional.softplus(lv["delta"] + bl), lv["A"], lv["B"], lv["C"],
+                                   lv["D"], z=lv["z"], h0=h0l, return_last_state=True)
+    yr.backward(inp["gy"].double())
+    tol = dict(rtol=1e-9, atol=1e-11)
+    assert torch.allclose(y, yr.detach(), **tol) and torch.allclose(hT, hTr.detach(), **tol)
+    for i, k in enumerate(("x", "delta", "z", "B", "C", "A", "D")):
+        assert torch.allclose(grads[i], lv[k].grad, **tol), k
+    assert torch.allclose(grads[7], bl.grad, **tol)
+    assert torch.allclose(grads[8], h0l.grad, **tol)
 
 
 def test_pick_subshards():
